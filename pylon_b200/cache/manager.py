@@ -9,8 +9,8 @@ and slots of fixed-size state per request.
   for a mixer that keeps one row per token), and for every request one table *logical page ->
   physical page*.
 * Pages are acquired just before the step that writes them (all of a step or none), given
-  back when the request is closed, and — in a windowed group — as soon as every position
-  on them lies behind the window of every token still to come.  Free pages are reused
+  back when the request is closed, and — in a group whose tokens read a window or only their
+  own chunk of positions — as soon as no token still to come can read any position on them.  Free pages are reused
   last-in first-out.
 * Every open request also holds a **slot**; mixers that keep a state of fixed size find
   theirs at ``state[slot]``.  States are zeroed when the slot is taken.  Qwen3 has none.
@@ -99,10 +99,11 @@ class CacheGroup:
         """Most pages a request of ``capacity`` tokens holds at any time in this group, when
         no step brings it more than ``max_step_tokens`` tokens."""
         full = self.pages_for(capacity)
-        if self.need.window is None:
+        if not self.need.bounded:
             return full
-        # A step's tokens plus the window before its first token, not page aligned.
-        span = min(capacity, self.need.window - 1 + max(1, max_step_tokens))
+        # A step's tokens plus what its first token reads before itself (a window, or the part of
+        # its chunk that lies before it), not page aligned.
+        span = min(capacity, self.need.reach - 1 + max(1, max_step_tokens))
         return min(full, self.pages_for(span) + 1)
 
     def bytes_per_token(self, element_size: Optional[int] = None) -> int:
@@ -138,7 +139,7 @@ def group_page_counts(needs: Sequence[Optional[CacheNeed]], page_size: int, pool
         if need is None or need.kv is None or need.kv in counts:
             continue
         pages = full
-        if need.kv.window is not None:
+        if need.kv.bounded:
             probe = CacheGroup(need.kv, [], PagePool(1), page_size)
             pages = min(full, max_requests * probe.lifetime_pages(longest_request, max_step_tokens))
         counts[need.kv] = max(1, pages)
@@ -287,10 +288,9 @@ class CacheManager:
         request.length += request.pending
         request.pending = 0
         for g, group in enumerate(self.groups):
-            window = group.need.window
-            if window is None:
+            if not group.need.bounded:
                 continue
-            first_needed = request.length - window + 1          # oldest key a later token reads
+            first_needed = group.need.first_needed(request.length)   # oldest key a later token reads
             dead_pages = max(0, first_needed) // self.page_size  # logical pages wholly before it
             table = request.tables[g]
             freed = [table[i] for i in range(min(dead_pages, len(table))) if table[i] >= 0]

@@ -14,7 +14,7 @@ from __future__ import annotations
 import json
 from dataclasses import asdict, dataclass, field
 from pathlib import Path
-from typing import Any, ClassVar, Mapping
+from typing import Any, ClassVar, Mapping, Optional
 
 
 class ConfigError(ValueError):
@@ -159,3 +159,140 @@ class Qwen3Config:
     @property
     def kv_size(self) -> int:
         return self.num_key_value_heads * self.head_dim
+
+
+# ---------------------------------------------------------------------------------------
+def _mapping(data: Mapping[str, Any], key: str) -> Mapping[str, Any]:
+    value = _require(data, key, dict)
+    return value
+
+
+def _number(data: Mapping[str, Any], key: str) -> float:
+    return float(_require(data, key, (int, float)))
+
+
+@dataclass(frozen=True)
+class VopepelLayer:
+    """One layer of a Vopepel model: which mixer (``delta`` or ``attention``) with its sizes, and its feed-forward
+    (``None``: the layer has none)."""
+
+    kind: str
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: Optional[int] = None          # delta: taps of the short convolution
+    scale: Optional[float] = None       # attention: factor on the scores
+    softcap: Optional[float] = None     # attention: scores go through softcap * tanh(score / softcap); None: no cap
+    chunk: Optional[int] = None         # attention: a token sees only keys of its own chunk of positions; None: all before it
+    v_mix: bool = False                 # attention: values are mixed with those of the first layer that says so
+    ff: Optional[int] = None            # feed-forward: inner width; None: no feed-forward
+    ff_kind: str = "dense"
+    ff_limit: Optional[float] = None
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], index: int) -> "VopepelLayer":
+        kind = _require(data, "type", str)
+        if kind not in ("delta", "attention"):
+            raise ConfigError(f"layer {index}: unknown type {kind!r} (delta, attention)")
+        mixer = _mapping(data, "mixer")
+        fields = dict(kind=kind, heads=_positive_int(mixer, "heads"), kv_heads=_positive_int(mixer, "kv_heads"),
+                      dim=_positive_int(mixer, "dim"), vdim=_positive_int(mixer, "vdim"))
+        if fields["heads"] % fields["kv_heads"]:
+            raise ConfigError(f"layer {index}: {fields['heads']} heads cannot be grouped over {fields['kv_heads']} kv_heads")
+        if kind == "delta":
+            fields["conv"] = _positive_int(mixer, "conv")
+        else:
+            fields["scale"] = _number(mixer, "scale")
+            if mixer.get("softcap") is not None:
+                fields["softcap"] = _number(mixer, "softcap")
+                if not fields["softcap"] > 0:
+                    raise ConfigError(f"layer {index}: softcap must be positive")
+            if mixer.get("mask") is not None:
+                fields["chunk"] = _positive_int(_mapping(mixer, "mask"), "size")
+            fields["v_mix"] = bool(mixer.get("v_mix", False))
+        mlp = data.get("mlp")
+        if mlp is not None:
+            if not isinstance(mlp, dict):
+                raise ConfigError(f"layer {index}: 'mlp' must be an object or null")
+            fields["ff_kind"] = str(mlp.get("kind", "dense"))
+            if fields["ff_kind"] != "dense":
+                raise ConfigError(f"layer {index}: feed-forward kind {fields['ff_kind']!r} is not built (dense)")
+            fields["ff"] = _positive_int(mlp, "ff")
+            fields["ff_limit"] = _number(mlp, "limit")
+            if not fields["ff_limit"] > 0:
+                raise ConfigError(f"layer {index}: the feed-forward's limit must be positive")
+        return cls(**fields)
+
+    def to_dict(self) -> dict[str, Any]:
+        mixer: dict[str, Any] = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim}
+        if self.kind == "delta":
+            mixer["conv"] = self.conv
+        else:
+            mixer["scale"] = self.scale
+            if self.softcap is not None:
+                mixer["softcap"] = self.softcap
+            if self.chunk is not None:
+                mixer["mask"] = {"size": self.chunk}
+            if self.v_mix:
+                mixer["v_mix"] = True
+        mlp = None if self.ff is None else {"kind": self.ff_kind, "ff": self.ff, "limit": self.ff_limit}
+        return {"type": self.kind, "mixer": mixer, "mlp": mlp}
+
+
+@dataclass(frozen=True)
+class VopepelConfig:
+    """Vopepel: a decoder whose layers are, in an order the configuration lists, gated-delta-rule mixers and chunked
+    soft-capped attention without positions, each with a clamped gated feed-forward (or none); layer norm without bias;
+    the residual stream optionally kept as several copies (hyper-connections); the sublayers' outputs times a factor.
+
+    ``config.json`` names the model by ``"architecture": "Vopepel"``.  Field names follow its keys.
+    """
+
+    architecture: ClassVar[str] = "Vopepel"
+
+    vocab: int
+    width: int
+    layers: tuple[VopepelLayer, ...]
+    norm_eps: float
+    residual_mult: float = 1.0
+    streams: Optional[int] = None      # copies of the residual stream; None: the plain residual sum
+    eos_token_ids: tuple[int, ...] = field(default_factory=tuple)
+
+    def __post_init__(self) -> None:
+        if not self.layers:
+            raise ConfigError("a model needs at least one layer")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.norm_eps}")
+        if self.streams is not None and not 1 <= self.streams <= 8:
+            raise ConfigError(f"streams must be 1 to 8, got {self.streams}")
+        mixing = [layer for layer in self.layers if layer.v_mix]
+        if any((layer.kv_heads, layer.vdim) != (mixing[0].kv_heads, mixing[0].vdim) for layer in mixing):
+            raise ConfigError("layers that mix values must have the same kv_heads and vdim")
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any]) -> "VopepelConfig":
+        layers = _require(data, "layers", list)
+        eos = data.get("eos_token_id")
+        streams = data.get("streams")
+        return cls(
+            vocab=_positive_int(data, "vocab"),
+            width=_positive_int(data, "width"),
+            layers=tuple(VopepelLayer.from_dict(layer, index) for index, layer in enumerate(layers)),
+            norm_eps=_number(_mapping(data, "norm"), "eps"),
+            residual_mult=float(data.get("residual_mult", 1.0)),
+            streams=None if streams is None else _positive_int(data, "streams"),
+            eos_token_ids=() if eos is None else ((eos,) if isinstance(eos, int) else tuple(int(x) for x in eos)),
+        )
+
+    def to_dict(self) -> dict[str, Any]:
+        data: dict[str, Any] = {
+            "architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+            "layers": [layer.to_dict() for layer in self.layers], "norm": {"eps": self.norm_eps},
+            "residual_mult": self.residual_mult,
+        }
+        if self.streams is not None:
+            data["streams"] = self.streams
+        if self.eos_token_ids:
+            data["eos_token_id"] = list(self.eos_token_ids)
+        return data

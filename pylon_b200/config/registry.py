@@ -11,7 +11,7 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Callable, Mapping, Optional
 
-from pylon_b200.config.model_config import ConfigError, Qwen3Config
+from pylon_b200.config.model_config import ConfigError, Qwen3Config, VopepelConfig
 from pylon_b200.parts.spec import ModelSpec
 
 
@@ -31,8 +31,10 @@ def register_architecture(name: str, config_class: Any, build_spec: Callable[[An
 
 def architecture_of(data: Mapping[str, Any]) -> Architecture:
     names = data.get("architectures")
+    if names is None and isinstance(data.get("architecture"), str):   # some formats name their one architecture in the singular
+        names = [data["architecture"]]
     if not isinstance(names, (list, tuple)) or len(names) != 1 or not isinstance(names[0], str):
-        raise ConfigError(f"config.json 'architectures' must name exactly one architecture, got {names!r}")
+        raise ConfigError(f"config.json 'architectures' (or 'architecture') must name exactly one architecture, got {names!r}")
     if names[0] not in ARCHITECTURES:
         raise ConfigError(f"unknown architecture '{names[0]}' (known: {', '.join(sorted(ARCHITECTURES))})")
     return ARCHITECTURES[names[0]]
@@ -57,6 +59,9 @@ def _register_builtin() -> None:
     from pylon_b200.models.qwen3 import qwen3_spec
 
     register_architecture(Qwen3Config.architecture, Qwen3Config, qwen3_spec)
+    from pylon_b200.models.vopepel import vopepel_spec
+
+    register_architecture(VopepelConfig.architecture, VopepelConfig, vopepel_spec)
 
 
 _register_builtin()

@@ -16,13 +16,16 @@ namespace pylon {
 // -----------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                    float* __restrict__ out, int width, int vocab, float scale) {
+                                    float* __restrict__ out, int width, int vocab, float scale, int copies) {
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host
   const T* row = table + (size_t)id * width;
-  float* dst = out + (size_t)t * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_float<T>(row[i]) * scale;   // scale is 1 for models that take the table as it is: exact
+  float* dst = out + (size_t)t * copies * width;     // a model with several residual streams starts all of them from the same row
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float value = to_float<T>(row[i]) * scale;   // scale is 1 for models that take the table as it is: exact
+    for (int c = 0; c < copies; ++c) dst[(size_t)c * width + i] = value;
+  }
 }
 
 // -----------------------------------------------------------------------------------------
@@ -570,8 +573,25 @@ __global__ void __launch_bounds__(128, 5) qk_norm_rope_kv_write_wide_kernel(
 // -----------------------------------------------------------------------------------------
 // `interleaved`: gate and up columns alternate in groups of 8 ([g0..g7 u0..u7 g8..g15 ...])
 // instead of lying in two halves.
+// `limit` > 0 selects the clamped form of the gated unit instead: g <- min(g, limit), u <- clamp(u, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + 1).
+template <bool EXACT>
+__device__ __forceinline__ float gated_unit(float g, float u, float limit, float alpha) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    const float e = EXACT ? expf(-alpha * g) : __expf(-alpha * g);
+    return (EXACT ? g / (1.f + e) : __fdividef(g, 1.f + e)) * (u + 1.f);
+  }
+  // float storage is the true 32-bit path: full-precision exponential there; the approximate division has no slow
+  // path (the exact one takes a subroutine for zero numerators), ample for a bfloat16 result
+  const float e = EXACT ? expf(-g) : __expf(-g);
+  return EXACT ? g / (1.f + e) * u : __fdividef(g, 1.f + e) * u;
+}
+
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, int interleaved) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, int interleaved,
+                              float limit, float alpha) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (; i < total; i += stride) {
@@ -581,15 +601,13 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     const int up_column = interleaved ? gate_column + 8 : inter + c;
     const float g = to_float<T>(gate_up[t * 2 * inter + gate_column]);
     const float u = to_float<T>(gate_up[t * 2 * inter + up_column]);
-    // float storage is the true 32-bit path: full-precision exponential there
-    const float e = sizeof(T) == 4 ? expf(-g) : __expf(-g);
-    out[i] = from_float<T>(g / (1.f + e) * u);
+    out[i] = from_float<T>(sizeof(T) == 4 ? gated_unit<true>(g, u, limit, alpha) : gated_unit<false>(g, u, limit, alpha));
   }
 }
 
 // Vector form for bfloat16 rows whose width is a multiple of 8 (16-byte accesses).
 __global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gate_up, uint4* __restrict__ out, int inter8,
-                                     size_t total8, int interleaved) {
+                                     size_t total8, int interleaved, float limit, float alpha) {
   grid_dependency_wait();
   allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -607,10 +625,81 @@ __global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gate_up, uint4* _
     for (int k = 0; k < 4; ++k) {
       const float2 g = __bfloat1622float2(g2[k]);
       const float2 u = __bfloat1622float2(u2[k]);
-      // approximate division: no slow path (the exact one takes a subroutine for zero numerators), ample for a bfloat16 result
-      o2[k] = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.f + __expf(-g.y)) * u.y);
+      o2[k] = __floats2bfloat162_rn(gated_unit<false>(g.x, u.x, limit, alpha), gated_unit<false>(g.y, u.y, limit, alpha));
     }
     out[i] = o4;
+  }
+}
+
+
+// -----------------------------------------------------------------------------------------
+// q/k RMSNorm + cache write for attention without rotation, whose values may have another
+// width than its keys and may be mixed with an earlier layer's values of the same token.
+// One warp per (token, head) of qkv [T, nq * d + nkv * d + nkv * dv]:
+//   q head : normalised (weight, eps) in place
+//   k head : normalised, written to its page slot [pages, nkv, page_size, d]
+//   v head : v <- (1 - lambda) v + lambda v_other[t] when v_other is given (lambda: a float32 on
+//            the device), written back in place and to its page slot [pages, nkv, page_size, dv]
+// v_other: rows of nkv * dv values with a row stride, in T; it may be another layer's qkv buffer.
+// -----------------------------------------------------------------------------------------
+template <typename T>
+__global__ void qk_norm_mix_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                                            float eps, const T* __restrict__ v_other, long long v_other_stride,
+                                            const float* __restrict__ lambda, const int* __restrict__ positions,
+                                            const int* __restrict__ token_row, const int* __restrict__ block_table, int table_width,
+                                            int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int nq,
+                                            int nkv, int d, int dv, int num_tokens, int* __restrict__ error) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const long long item = (long long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long long)num_tokens * heads) return;
+  const int t = (int)(item / heads), head = (int)(item % heads);
+  const long long ld = (long long)(nq + nkv) * d + (long long)nkv * dv;
+  T* row_base = qkv + (long long)t * ld;
+  T* page_dst = nullptr;
+  const bool is_value = head >= nq + nkv;
+  if (head >= nq) {
+    const int row = token_row[t];
+    if (row < 0) return;   // a padding token: it belongs to no request
+    const int pos = positions[t];
+    const int page = block_table[(size_t)row * table_width + pos / page_size];
+    if (page < 0 || page >= num_pages) {   // never for a prepared step: nothing is written, and the host is told
+      if (lane == 0 && error) atomicExch(error, PYLON_ERROR_BAD_PAGE);
+      return;
+    }
+    const int kv_head = is_value ? head - nq - nkv : head - nq;
+    const int width = is_value ? dv : d;
+    page_dst = (is_value ? v_pages : k_pages) + (((size_t)page * nkv + kv_head) * page_size + pos % page_size) * width;
+  }
+  if (is_value) {
+    const int kv_head = head - nq - nkv;
+    T* src = row_base + (long long)(nq + nkv) * d + (long long)kv_head * dv;
+    const float lam = v_other ? lambda[0] : 0.f;
+    const T* other = v_other ? v_other + (long long)t * v_other_stride + (long long)kv_head * dv : nullptr;
+    for (int e = lane; e < dv; e += 32) {
+      T value = src[e];
+      if (other) {
+        value = from_float<T>((1.f - lam) * to_float<T>(value) + lam * to_float<T>(other[e]));
+        src[e] = value;
+      }
+      page_dst[e] = value;
+    }
+    return;
+  }
+  T* src = row_base + (long long)head * d;
+  const float* weight = head < nq ? q_weight : k_weight;
+  float sumsq = 0.f;
+  for (int e = lane; e < d; e += 32) {
+    const float x = to_float<T>(src[e]);
+    sumsq = fmaf(x, x, sumsq);
+  }
+  sumsq = warp_sum(sumsq);
+  const float inv = weight ? rsqrtf(sumsq / (float)d + eps) : 1.f;
+  T* dst = head < nq ? src : page_dst;
+  for (int e = lane; e < d; e += 32) {
+    const float x = to_float<T>(src[e]);
+    dst[e] = from_float<T>(weight ? x * inv * weight[e] : x);
   }
 }
 
@@ -646,14 +735,14 @@ extern "C" int pylon_take_tokens(int* ids, const int* source, const int* sampled
 }
 
 extern "C" int pylon_embed_gather(const int* ids, const void* table, float* out, int num_tokens, int width,
-                                  int vocab, int dtype, float scale, cudaStream_t stream) {
+                                  int vocab, int dtype, float scale, int copies, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  if (width <= 0 || vocab <= 0) PYLON_REFUSE("embed_gather: width %d, vocab %d", width, vocab);
+  if (width <= 0 || vocab <= 0 || copies < 1) PYLON_REFUSE("embed_gather: width %d, vocab %d, copies %d", width, vocab, copies);
   const int threads = width >= 1024 ? 256 : 128;
   if (dtype == PYLON_DTYPE_F32)
-    embed_gather_kernel<float><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, width, vocab, scale);
+    embed_gather_kernel<float><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, width, vocab, scale, copies);
   else if (dtype == PYLON_DTYPE_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, width, vocab, scale);
+    embed_gather_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, width, vocab, scale, copies);
   else
     PYLON_REFUSE("embed_gather: unknown dtype %d", dtype);
   PYLON_CHECK_LAUNCH("embed_gather");
@@ -847,8 +936,9 @@ extern "C" int pylon_qk_norm_rope_kv_write_parts(const float* qkv_parts, int par
 }
 
 extern "C" int pylon_swiglu(const void* gate_up, void* out, int num_tokens, int inter, int interleaved, int dtype,
-                            cudaStream_t stream) {
+                            float limit, float alpha, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
+  if (limit < 0.f) PYLON_REFUSE("swiglu: limit %f", limit);
   if (inter <= 0) PYLON_REFUSE("swiglu: intermediate size %d", inter);
   if (interleaved && inter % 8) PYLON_REFUSE("swiglu: the interleaved layout needs an intermediate size that is a multiple of 8, not %d", inter);
   const size_t total = (size_t)num_tokens * inter;
@@ -856,13 +946,46 @@ extern "C" int pylon_swiglu(const void* gate_up, void* out, int num_tokens, int 
   const size_t most = (size_t)pylon::multiprocessors() * 32;
   auto grid = [&](size_t n) { size_t b = (n + threads - 1) / threads; return (int)(b < most ? b : most); };
   if (dtype == PYLON_DTYPE_BF16 && inter % 8 == 0 && ((uintptr_t)gate_up % 16 == 0) && ((uintptr_t)out % 16 == 0)) {
-    launch_dependent(swiglu_bf16x8_kernel, dim3(grid(total / 8)), dim3(threads), 0, stream, (const uint4*)gate_up, (uint4*)out, inter / 8, total / 8, interleaved);
+    launch_dependent(swiglu_bf16x8_kernel, dim3(grid(total / 8)), dim3(threads), 0, stream, (const uint4*)gate_up, (uint4*)out, inter / 8, total / 8, interleaved, limit, alpha);
   } else if (dtype == PYLON_DTYPE_BF16) {
-    swiglu_kernel<__nv_bfloat16><<<grid(total), threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total, interleaved);
+    swiglu_kernel<__nv_bfloat16><<<grid(total), threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total, interleaved, limit, alpha);
   } else if (dtype == PYLON_DTYPE_F32) {
-    swiglu_kernel<float><<<grid(total), threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total, interleaved);
+    swiglu_kernel<float><<<grid(total), threads, 0, stream>>>((const float*)gate_up, (float*)out, inter, total, interleaved, limit, alpha);
   } else {
     PYLON_REFUSE("swiglu: unknown dtype %d", dtype);
   }
   PYLON_CHECK_LAUNCH("swiglu");
+}
+
+template <typename T>
+static int launch_qk_norm_mix(void* qkv, const float* qw, const float* kw, float eps, const void* v_other, long long v_other_stride,
+                              const float* lambda, const int* positions, const int* token_row, const int* block_table, int table_width,
+                              int page_size, void* k_pages, void* v_pages, int num_pages, int nq, int nkv, int d, int dv, int num_tokens,
+                              int* error, cudaStream_t stream) {
+  const int warps = 4;
+  const long long items = (long long)num_tokens * (nq + 2 * nkv);
+  qk_norm_mix_kv_write_kernel<T><<<(unsigned)((items + warps - 1) / warps), warps * 32, 0, stream>>>(
+      (T*)qkv, qw, kw, eps, (const T*)v_other, v_other_stride, lambda, positions, token_row, block_table, table_width, page_size,
+      (T*)k_pages, (T*)v_pages, num_pages, nq, nkv, d, dv, num_tokens, error);
+  PYLON_CHECK_LAUNCH("qk_norm_mix_kv_write");
+}
+
+// See qk_norm_mix_kv_write_kernel.  A null weight leaves its heads as they are; a null v_other mixes nothing.
+extern "C" int pylon_qk_norm_mix_kv_write(void* qkv, const float* q_weight, const float* k_weight, float eps, const void* v_other,
+                                          long long v_other_stride, const float* lambda, const int* positions, const int* token_row,
+                                          const int* block_table, int table_width, int page_size, void* k_pages, void* v_pages,
+                                          int num_pages, int nq, int nkv, int d, int dv, int num_tokens, int dtype, int* error,
+                                          cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (d < 1 || dv < 1 || nq < 0 || nkv < 1 || page_size < 1 || table_width < 1)
+    PYLON_REFUSE("qk_norm_mix_kv_write: sizes %d/%d, heads %d/%d, page size %d, table width %d", d, dv, nq, nkv, page_size, table_width);
+  if ((v_other == nullptr) != (lambda == nullptr)) PYLON_REFUSE("qk_norm_mix_kv_write: other values and their weight go together");
+  if (dtype == PYLON_DTYPE_F32)
+    return launch_qk_norm_mix<float>(qkv, q_weight, k_weight, eps, v_other, v_other_stride, lambda, positions, token_row, block_table,
+                                     table_width, page_size, k_pages, v_pages, num_pages, nq, nkv, d, dv, num_tokens, error, stream);
+  if (dtype == PYLON_DTYPE_BF16)
+    return launch_qk_norm_mix<__nv_bfloat16>(qkv, q_weight, k_weight, eps, v_other, v_other_stride, lambda, positions, token_row,
+                                             block_table, table_width, page_size, k_pages, v_pages, num_pages, nq, nkv, d, dv, num_tokens,
+                                             error, stream);
+  PYLON_REFUSE("qk_norm_mix_kv_write: unknown dtype %d", dtype);
 }

@@ -88,7 +88,7 @@ class Engine:
                 max_requests=self.config.max_batch_size, dtype=dtype, device=self.device,
             )
         # a request can be as long as the groups that keep every key have room for
-        keeps_all = [group.pool.num_pages * page_size for group in self.cache.groups if group.need.window is None]
+        keeps_all = [group.pool.num_pages * page_size for group in self.cache.groups if not group.need.bounded]
         self.max_context = min([self.spec.max_positions] + keeps_all)
         self.step_function = StepFunction(self.model, self.cache)
         if self.config.cuda_graphs:
@@ -124,13 +124,13 @@ class Engine:
         free, total = torch.cuda.mem_get_info(self.device)
         activation_room = chunk * self.spec.width * 64
         budget = int(total * self.config.max_gpu_utilization) - (total - free) - activation_room
-        windowed = {kv: pages for kv, pages in most.items() if kv.window is not None}
+        windowed = {kv: pages for kv, pages in most.items() if kv.bounded}
         budget -= sum(pages * page_bytes[kv] for kv, pages in windowed.items())
-        shared = sum(size for kv, size in page_bytes.items() if kv.window is None)
+        shared = sum(size for kv, size in page_bytes.items() if not kv.bounded)
         pages = budget // shared if shared else 0
         if budget < 0 or (shared and pages < 1):
             raise RuntimeError("no memory is left for the cache after loading the weights")
-        return {kv: (count if kv.window is not None else int(min(pages, count))) for kv, count in most.items()}
+        return {kv: (count if kv.bounded else int(min(pages, count))) for kv, count in most.items()}
 
     # -- the step function, for callers that batch themselves --------------------------------
     def open(self, request_id: object, capacity: int) -> RequestCache:

@@ -164,7 +164,7 @@ def raise_on_kernel_errors(device: torch.device, queued: bool = False, words: Op
 
 _SIGNATURES = {
     "elementwise.cu": {
-        "pylon_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
+        "pylon_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "pylon_take_tokens": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "pylon_logit_transform": [c_void_p, c_longlong, c_float, c_float, c_void_p],
         "pylon_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
@@ -177,7 +177,18 @@ _SIGNATURES = {
                                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                               c_int, c_void_p, c_void_p],
         "pylon_qk_norm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
-        "pylon_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+        "pylon_qk_norm_mix_kv_write": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    },
+    "streams.cu": {
+        "pylon_streams_update_norm": [c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    },
+    "delta_rule.cu": {
+        "pylon_gated_delta_rule": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_float, c_float, c_int, c_int, c_int, c_void_p],
     },
     "gemm_f32.cu": {
         "pylon_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
@@ -200,7 +211,7 @@ _SIGNATURES = {
     },
     "attention_simple.cu": {
         "pylon_paged_attention_simple": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
                                          c_int, c_int, c_void_p],
     },
     "attention_mma.cu": {
@@ -252,17 +263,19 @@ def build_all() -> list[str]:
 # ---------------------------------------------------------------------------------------
 # embedding, norms, residual
 # ---------------------------------------------------------------------------------------
-def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
-    """float32 ``[T, width]`` rows of ``table`` (``[vocab, width]``) picked by int32 ``ids``, times ``scale``."""
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0, copies: int = 1) -> torch.Tensor:
+    """float32 ``[T, width]`` rows of ``table`` (``[vocab, width]``) picked by int32 ``ids``, times ``scale``.  With
+    ``copies`` > 1 the result is ``[T, copies, width]``, every copy the same row (a model with several residual streams)."""
     _need_cuda(ids, table, out)
     _need(ids.dtype == torch.int32 and ids.dim() == 1 and ids.is_contiguous(), "embed_gather: ids must be contiguous int32 [T]")
     _need(table.dim() == 2 and table.is_contiguous(), "embed_gather: table must be contiguous [vocab, width]")
     tokens, (vocab, width) = ids.shape[0], table.shape
+    shape = (tokens, width) if copies == 1 else (tokens, int(copies), width)
     if out is None:
-        out = torch.empty((tokens, width), dtype=torch.float32, device=table.device)
-    _need(out.dtype == torch.float32 and out.shape == (tokens, width) and out.is_contiguous(), "embed_gather: out must be contiguous float32 [T, width]")
+        out = torch.empty(shape, dtype=torch.float32, device=table.device)
+    _need(out.dtype == torch.float32 and out.shape == shape and out.is_contiguous(), "embed_gather: out must be contiguous float32 [T, width] or [T, copies, width]")
     library = _library("elementwise.cu")
-    _check(library, library.pylon_embed_gather(_ptr(ids), _ptr(table), _ptr(out), tokens, width, vocab, _dtype_code(table.dtype), float(scale), _stream()))
+    _check(library, library.pylon_embed_gather(_ptr(ids), _ptr(table), _ptr(out), tokens, width, vocab, _dtype_code(table.dtype), float(scale), int(copies), _stream()))
     return out
 
 
@@ -422,11 +435,14 @@ def qk_norm(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: Optio
     return qkv
 
 
-def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, interleaved: bool = False) -> torch.Tensor:
+def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, interleaved: bool = False,
+           limit: Optional[float] = None, alpha: float = 1.0) -> torch.Tensor:
     """``silu(gate) * up`` for ``gate_up`` of shape ``[T, 2 * inter]``: ``[gate | up]`` in two
     halves, or with ``interleaved`` in alternating groups of 8 columns
     (``[g0..g7 u0..u7 g8..g15 u8..u15 ...]``, the layout :func:`interleave_gate_up` gives the
-    weights)."""
+    weights).  With a ``limit`` the gated unit is the clamped one: ``g = min(gate, limit)``,
+    ``u = clamp(up, -limit, limit)``, result ``g * sigmoid(alpha * g) * (u + 1)``."""
+    _need(limit is None or limit > 0, "swiglu: a limit must be positive")
     _need_cuda(gate_up, out)
     _need(gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0, "swiglu: gate_up must be contiguous [T, 2 * inter]")
     tokens, inter = gate_up.shape[0], gate_up.shape[1] // 2
@@ -434,7 +450,8 @@ def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, interleave
         out = torch.empty((tokens, inter), dtype=gate_up.dtype, device=gate_up.device)
     _need(out.shape == (tokens, inter) and out.dtype == gate_up.dtype and out.is_contiguous(), "swiglu: out has the wrong shape or dtype")
     library = _library("elementwise.cu")
-    _check(library, library.pylon_swiglu(_ptr(gate_up), _ptr(out), tokens, inter, int(interleaved), _dtype_code(gate_up.dtype), _stream()))
+    _check(library, library.pylon_swiglu(_ptr(gate_up), _ptr(out), tokens, inter, int(interleaved), _dtype_code(gate_up.dtype),
+                                         float(limit or 0.0), float(alpha), _stream()))
     return out
 
 
@@ -756,8 +773,14 @@ def paged_attention(
     prefill_kernel: Optional[str] = None,
     row_tokens: Optional[Sequence[int]] = None,
     rows_alike: bool = False,
+    chunk: Optional[int] = None,
+    softcap: Optional[float] = None,
 ) -> torch.Tensor:
     """Causal attention of every token of a step over its request's pages.
+
+    ``chunk``: a token sees only the keys of its own chunk of positions (``j // chunk == p // chunk``,
+    counted from position 0 of the request).  ``softcap`` c: a scaled score s becomes ``c * tanh(s / c)``.
+    The value pages may have another row width than the key pages; the result is ``[T, nq * value width]``.
 
     ``q``: ``[T, >= nq * d]`` (only the first ``nq * d`` columns of each row are read, so
     the fused qkv buffer can be passed as it is); pages ``[P, nkv, page_size, d]``;
@@ -783,8 +806,13 @@ def paged_attention(
     to 512, take the plain kernel.
     """
     _need_cuda(q, k_pages, v_pages, positions, token_row, q_start, kv_len, block_table, out)
-    _need(k_pages.dim() == 4 and k_pages.shape == v_pages.shape and k_pages.is_contiguous() and v_pages.is_contiguous(), "paged_attention: pages must be contiguous [P, nkv, page_size, d]")
+    _need(k_pages.dim() == 4 and v_pages.dim() == 4 and k_pages.shape[:3] == v_pages.shape[:3] and k_pages.is_contiguous() and v_pages.is_contiguous()
+          and k_pages.dtype == v_pages.dtype, "paged_attention: pages must be contiguous [P, nkv, page_size, d] and [P, nkv, page_size, value width]")
     num_pages, nkv, page_size, d = k_pages.shape
+    dv = v_pages.shape[3]
+    _need(chunk is None or chunk >= 1, "paged_attention: a chunk holds at least one position")
+    _need(softcap is None or softcap > 0, "paged_attention: a soft cap must be positive")
+    plain_scores = chunk is None and softcap is None and dv == d
     tokens = q.shape[0]
     _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= nq * d and q.dtype == k_pages.dtype, "paged_attention: q must be [T, >= nq * d] in the cache dtype")
     _need(nq % nkv == 0, f"paged_attention: {nq} query heads over {nkv} KV heads")
@@ -795,11 +823,11 @@ def paged_attention(
     _need(q_start.dtype == torch.int32 and q_start.is_contiguous() and q_start.shape[0] >= rows + 1, "paged_attention: q_start must be int32 [rows + 1]")
     _need(kv_len.dtype == torch.int32 and kv_len.is_contiguous() and kv_len.shape[0] >= rows, "paged_attention: kv_len must be int32 [rows]")
     if out is None:
-        out = torch.empty((tokens, nq * d), dtype=q.dtype, device=q.device)
-    _need(out.shape == (tokens, nq * d) and out.dtype == q.dtype and out.is_contiguous(), "paged_attention: out has the wrong shape or dtype")
+        out = torch.empty((tokens, nq * dv), dtype=q.dtype, device=q.device)
+    _need(out.shape == (tokens, nq * dv) and out.dtype == q.dtype and out.is_contiguous(), "paged_attention: out has the wrong shape or dtype")
     scale = 1.0 / math.sqrt(d) if scale is None else float(scale)
     _need(scale > 0, "paged_attention: the softmax scale must be positive")
-    if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and not force_simple:
+    if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and not force_simple and plain_scores:
         library = _library("attention_mma.cu", {"PYLON_HEAD_DIM": d})
         group = nq // nkv
         any_large = max_q * group > 16
@@ -842,11 +870,178 @@ def paged_attention(
             _ptr(block_table), block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), scale, rows, tokens,
             int(max_q), splits, blocks, int(use_tcgen05), int(bool(rows_alike)), _ptr(attention_error_word(q.device)), _stream()))
         return out
-    _need(d <= 512, f"paged_attention: head size {d} is larger than 512")
+    _need(d <= 512 and dv <= 512, f"paged_attention: head sizes {d} / {dv}: at most 512")
     library = _library("attention_simple.cu")
     _check(library, library.pylon_paged_attention_simple(
         _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(positions), _ptr(token_row), _ptr(block_table),
-        block_table.shape[1], page_size, num_pages, nq, nkv, d, int(window or 0), scale, tokens, _dtype_code(q.dtype), _stream()))
+        block_table.shape[1], page_size, num_pages, nq, nkv, d, dv, int(window or 0), int(chunk or 0), float(softcap or 0.0), scale, tokens,
+        _dtype_code(q.dtype), _stream()))
+    return out
+
+
+def qk_norm_mix_kv_write(
+    qkv: torch.Tensor,
+    q_weight: Optional[torch.Tensor],
+    k_weight: Optional[torch.Tensor],
+    eps: float,
+    positions: torch.Tensor,
+    token_row: torch.Tensor,
+    block_table: torch.Tensor,
+    page_size: int,
+    k_pages: torch.Tensor,
+    v_pages: torch.Tensor,
+    nq: int,
+    nkv: int,
+    head_dim: int,
+    value_dim: int,
+    other_values: Optional[torch.Tensor] = None,
+    mix_weight: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """For attention without rotation, on ``qkv [T, nq * d + nkv * d + nkv * dv]``: RMSNorm each q and k head (when
+    weights are given), q back in place, k into its page slot; every v head, mixed first with another layer's values
+    of the same token when ``other_values [T, >= nkv * dv]`` (any row stride) and ``mix_weight`` (one float32 on the
+    device, the share of the other values) are given - ``v = (1 - w) v + w other`` -, back in place and into its page
+    slot.  Returns ``qkv``: its first ``nq * d`` columns hold q, its last ``nkv * dv`` the values that were kept."""
+    _need_cuda(qkv, q_weight, k_weight, positions, token_row, block_table, k_pages, v_pages, other_values, mix_weight)
+    tokens = qkv.shape[0]
+    _need(qkv.dim() == 2 and qkv.is_contiguous() and qkv.shape[1] == (nq + nkv) * head_dim + nkv * value_dim, "qk_norm_mix_kv_write: qkv must be contiguous [T, nq d + nkv d + nkv dv]")
+    for weight in (q_weight, k_weight):
+        if weight is not None:
+            _need(weight.dtype == torch.float32 and weight.shape == (head_dim,) and weight.is_contiguous(), "qk_norm_mix_kv_write: norm weights must be float32 [d]")
+    for meta in (positions, token_row):
+        _need(meta.dtype == torch.int32 and meta.is_contiguous() and meta.shape[0] >= tokens, "qk_norm_mix_kv_write: positions/token_row must be int32 [T]")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), "qk_norm_mix_kv_write: block_table must be contiguous int32 [rows, width]")
+    for pages, width in ((k_pages, head_dim), (v_pages, value_dim)):
+        _need(pages.dtype == qkv.dtype and pages.is_contiguous() and pages.dim() == 4 and pages.shape[1:] == (nkv, page_size, width),
+              "qk_norm_mix_kv_write: pages must be contiguous [pages, nkv, page_size, width] in the activation dtype")
+    _need((other_values is None) == (mix_weight is None), "qk_norm_mix_kv_write: other values and their weight go together")
+    other_stride = 0
+    if other_values is not None:
+        _need(other_values.dim() == 2 and other_values.shape == (tokens, nkv * value_dim) and other_values.stride(1) == 1 and other_values.dtype == qkv.dtype,
+              "qk_norm_mix_kv_write: other values must be [T, nkv * dv] in the activation dtype")
+        _need(mix_weight.dtype == torch.float32 and mix_weight.numel() == 1, "qk_norm_mix_kv_write: the mixing weight is one float32")
+        other_stride = other_values.stride(0)
+    library = _library("elementwise.cu")
+    _check(library, library.pylon_qk_norm_mix_kv_write(
+        _ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(other_values), other_stride, _ptr(mix_weight), _ptr(positions),
+        _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], nq, nkv,
+        head_dim, value_dim, tokens, _dtype_code(qkv.dtype), _ptr(cache_write_error_word(k_pages.device)), _stream()))
+    return qkv
+
+
+# ---------------------------------------------------------------------------------------
+# residual streams (one or several) and the norms that read them
+# ---------------------------------------------------------------------------------------
+NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
+
+
+def streams_update_norm(
+    streams: torch.Tensor,
+    delta: Optional[torch.Tensor],
+    scale: float = 1.0,
+    mix: Optional[torch.Tensor] = None,
+    out_weights: Optional[torch.Tensor] = None,
+    read_weights: Optional[torch.Tensor] = None,
+    norm_weight: Optional[torch.Tensor] = None,
+    eps: float = 0.0,
+    kind: str = "layernorm",
+    out_dtype: Optional[torch.dtype] = None,
+    rows: Optional[torch.Tensor] = None,
+) -> Optional[torch.Tensor]:
+    """The residual stream kept as ``S`` copies, float32 ``[T, S, width]`` (``[T, width]`` is one copy).
+
+    First, if anything is pending (``delta``, the sublayer output ``[T, width]`` in the activation dtype or float32
+    partial sums ``[parts, T, width]``; or a ``mix``), all streams at once from the old ones:
+    ``x_t = sum_s mix[s, t] x_s + scale * out_weights[t] * delta`` (``mix`` float32 ``[S, S]``, ``None`` = identity;
+    ``out_weights`` float32 ``[S]``, ``None`` = ones), in place.  Then, with a ``norm_weight``, the combination
+    ``u = sum_s read_weights[s] x_s`` (``None`` = the plain sum) goes through the norm (``layernorm``: mean subtracted,
+    variance the mean of squared deviations, no bias; ``rmsnorm``) and comes back ``[T, width]`` in ``out_dtype``.
+    With ``rows`` (int32) only those tokens are normalised, from updated values computed on the fly; the streams stay
+    as they are."""
+    _need_cuda(streams, delta, mix, out_weights, read_weights, norm_weight, rows)
+    _need(streams.dtype == torch.float32 and streams.is_contiguous() and streams.dim() in (2, 3), "streams_update_norm: streams must be contiguous float32 [T, S, width] or [T, width]")
+    tokens, width = streams.shape[0], streams.shape[-1]
+    count = 1 if streams.dim() == 2 else streams.shape[1]
+    parts, delta_code = 1, F32
+    if delta is not None:
+        _need(delta.is_contiguous() and delta.shape[-2:] == (tokens, width) and delta.dim() in (2, 3), "streams_update_norm: delta must be contiguous [T, width] or [parts, T, width]")
+        parts = delta.shape[0] if delta.dim() == 3 else 1
+        delta_code = _dtype_code(delta.dtype)
+    for name, tensor, shape in (("mix", mix, (count, count)), ("out_weights", out_weights, (count,)), ("read_weights", read_weights, (count,)),
+                                ("norm_weight", norm_weight, (width,))):
+        if tensor is not None:
+            _need(tensor.dtype == torch.float32 and tuple(tensor.shape) == shape and tensor.is_contiguous(), f"streams_update_norm: {name} must be contiguous float32 {shape}")
+    _need(kind in NORM_KINDS, f"streams_update_norm: unknown norm kind {kind!r}")
+    n_rows = tokens
+    if rows is not None:
+        _need(rows.dtype == torch.int32 and rows.dim() == 1 and rows.is_contiguous(), "streams_update_norm: rows must be contiguous int32")
+        _need(norm_weight is not None, "streams_update_norm: a row selection needs a norm")
+        n_rows = rows.shape[0]
+    out = None
+    if norm_weight is not None:
+        _need(out_dtype is not None, "streams_update_norm: a norm needs an output dtype")
+        out = torch.empty((n_rows, width), dtype=out_dtype, device=streams.device)
+    elif delta is None and mix is None:
+        return None
+    library = _library("streams.cu")
+    _check(library, library.pylon_streams_update_norm(
+        _ptr(streams), _ptr(delta), parts, delta_code, float(scale), _ptr(mix), _ptr(out_weights), _ptr(read_weights), _ptr(norm_weight),
+        _ptr(rows), _ptr(out), _dtype_code(out_dtype) if out is not None else F32, n_rows, tokens, count, width, float(eps), NORM_KINDS[kind], _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# gated delta rule
+# ---------------------------------------------------------------------------------------
+def gated_delta_rule(
+    proj: torch.Tensor,
+    conv_weight: torch.Tensor,
+    state: torch.Tensor,
+    token_row: torch.Tensor,
+    q_start: torch.Tensor,
+    slots: torch.Tensor,
+    a_log: torch.Tensor,
+    dt_bias: torch.Tensor,
+    norm_weight: torch.Tensor,
+    heads: int,
+    kv_heads: int,
+    dim: int,
+    vdim: int,
+    num_rows: int,
+    norm_eps: float,
+    unit_eps: float = 1e-6,
+) -> torch.Tensor:
+    """The gated delta rule over the tokens of a step (see ``csrc/delta_rule.cu`` for the equations).
+
+    ``proj [T, 2 kv_heads dim + 2 heads vdim + 2 heads]``: the projections of the layer's input with columns
+    ``[q | k | v | gate | a | b]``; ``conv_weight`` float32 ``[channels, taps]`` over the q, k, v columns; ``state`` float32
+    ``[slots, heads * dim * vdim + (taps - 1) * channels]``: per request the heads' matrices and the convolution's last
+    inputs, read at ``state[slots[row]]`` and advanced in place by the row's tokens; ``a_log``, ``dt_bias`` float32
+    ``[heads]``; ``norm_weight`` float32 ``[vdim]``.  Returns ``[T, heads * vdim]`` in ``proj``'s dtype: the read-out,
+    normalised per head and gated, ready for the output projection."""
+    _need_cuda(proj, conv_weight, state, token_row, q_start, slots, a_log, dt_bias, norm_weight)
+    channels = 2 * kv_heads * dim + heads * vdim
+    columns = channels + heads * vdim + 2 * heads
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] == columns, f"gated_delta_rule: proj must be [T, {columns}]")
+    tokens = proj.shape[0]
+    _need(conv_weight.dtype == torch.float32 and conv_weight.dim() == 2 and conv_weight.shape[0] == channels and conv_weight.is_contiguous(),
+          "gated_delta_rule: conv_weight must be contiguous float32 [channels, taps]")
+    taps = conv_weight.shape[1]
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous(), "gated_delta_rule: state must be contiguous float32 [slots, floats]")
+    for name, tensor, size in (("a_log", a_log, heads), ("dt_bias", dt_bias, heads), ("norm_weight", norm_weight, vdim)):
+        _need(tensor.dtype == torch.float32 and tensor.shape == (size,) and tensor.is_contiguous(), f"gated_delta_rule: {name} must be float32 [{size}]")
+    for name, tensor, size in (("token_row", token_row, tokens), ("q_start", q_start, num_rows + 1), ("slots", slots, num_rows)):
+        _need(tensor.dtype == torch.int32 and tensor.is_contiguous() and tensor.shape[0] >= size, f"gated_delta_rule: {name} must be int32 [{size}]")
+    qkv = torch.empty((tokens, channels), dtype=torch.float32, device=proj.device)
+    gates = torch.empty((tokens, 2 * heads), dtype=torch.float32, device=proj.device)
+    read = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=proj.device)
+    out = torch.empty((tokens, heads * vdim), dtype=proj.dtype, device=proj.device)
+    library = _library("delta_rule.cu")
+    _check(library, library.pylon_gated_delta_rule(
+        _ptr(proj), proj.stride(0), _ptr(conv_weight), taps, _ptr(state), state.shape[1], _ptr(token_row), _ptr(q_start), _ptr(slots),
+        _ptr(qkv), _ptr(gates), _ptr(read), _ptr(out), _ptr(a_log), _ptr(dt_bias), _ptr(norm_weight), channels + heads * vdim,
+        channels + heads * vdim + heads, channels, heads, kv_heads, dim, vdim, float(unit_eps), float(norm_eps), tokens, num_rows,
+        _dtype_code(proj.dtype), _stream()))
     return out
 
 

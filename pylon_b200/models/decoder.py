@@ -39,13 +39,13 @@ class DecoderModel:
             decls[spec.lm_head_name] = TensorDecl(spec.lm_head_name, (spec.vocab_size, spec.width))
         for decl in self.final_norm.tensors():
             name = spec.final_norm_prefix + decl.name
-            decls[name] = TensorDecl(name, decl.shape, decl.role)
+            decls[name] = TensorDecl(name, decl.shape, decl.role, decl.init)
         for layer, block in zip(spec.layers, self.blocks):
             for decl in block.tensors():
                 name = layer.prefix + decl.name
                 if name in decls:
                     raise ValueError(f"two parts declare the tensor '{name}'")
-                decls[name] = TensorDecl(name, decl.shape, decl.role)
+                decls[name] = TensorDecl(name, decl.shape, decl.role, decl.init)
         return decls
 
     def load(self, fetch: Callable[[str], torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
@@ -88,14 +88,19 @@ class DecoderModel:
         ]
 
     # -- run -----------------------------------------------------------------------------
-    def forward(self, step: StepView, caches: Sequence[LayerCache]) -> Optional[torch.Tensor]:
+    def forward(self, step: StepView, caches: Sequence[LayerCache], taps: Optional[list] = None) -> Optional[torch.Tensor]:
         """Runs the step's tokens; returns float32 logits ``[num_logits, vocab]`` at
         ``step.logit_rows`` (``None`` when no logits are wanted: the head is skipped).
-        ``caches[i]`` belongs to run ``i`` of the order (a shared cache appears twice)."""
-        residual = ops.embed_gather(step.token_ids, self.embedding, scale=self.spec.embedding_scale)
+        ``caches[i]`` belongs to run ``i`` of the order (a shared cache appears twice).
+        ``taps``: a list that receives the residual stream after every run, float32 ``[T, width]``
+        (the sum of the copies where the model keeps several) - for looking at a model layer by layer."""
+        step.carry = {}
+        residual = ops.embed_gather(step.token_ids, self.embedding, scale=self.spec.embedding_scale, copies=self.spec.streams)
         stream = ResidualStream(residual)
         for position, run in enumerate(self.spec.order):
             self.blocks[run.layer].forward(stream, step, caches[position])
+            if taps is not None:
+                taps.append(stream.total().clone())
         if step.num_logits == 0:
             return None
         hidden = self.final_norm.apply(stream, rows=step.logit_rows)

@@ -5,6 +5,13 @@ position encoding, the write of k and v into the layer's pages, causal (optional
 windowed) attention over the pages, and the output product.  Order of operations as in
 raun6k/Pylon's ``GroupedQueryAttention`` (src/pylon/model/layers.py:81-138) with its cache
 write before attention (src/pylon/kv/cache.py:457-476).
+
+Options beyond that: values of another width than the keys (``value_dim``); a soft cap on the
+scaled scores, ``s -> c * tanh(s / c)`` (``softcap``); attention in chunks of positions, where a
+token sees the keys ``j <= i`` with ``j // chunk == i // chunk`` only, chunks counted from position
+0 of the request (``chunk``); and value mixing (``value_mix``): the layer that says ``"source"``
+leaves its values in the step under ``value_mix_key``, a layer that says ``"mix"`` replaces its own
+values by ``(1 - w) v + w v_source`` of the same token, with w a learnt scalar, before they are cached.
 """
 from __future__ import annotations
 
@@ -35,20 +42,36 @@ class GroupedQueryAttention(Mixer):
         window: Optional[int] = None,
         scale: Optional[float] = None,
         names: Optional[Mapping[str, str]] = None,
+        value_dim: Optional[int] = None,
+        chunk: Optional[int] = None,
+        softcap: Optional[float] = None,
+        value_mix: Optional[str] = None,
+        value_mix_key: str = "values",
     ) -> None:
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads cannot be grouped over {n_kv_heads} KV heads")
         self.width, self.n_heads, self.n_kv_heads, self.head_dim = int(width), int(n_heads), int(n_kv_heads), int(head_dim)
+        self.value_dim = self.head_dim if value_dim is None else int(value_dim)
         self.q_size, self.kv_size = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        self.v_size, self.out_size = self.n_kv_heads * self.value_dim, self.n_heads * self.value_dim
+        self.chunk = None if chunk is None else int(chunk)
+        self.softcap = None if softcap is None else float(softcap)
+        if value_mix not in (None, "source", "mix"):
+            raise ValueError(f"value_mix is 'source', 'mix' or None, not {value_mix!r}")
+        if (self.chunk is not None and self.chunk < 1) or (self.softcap is not None and not self.softcap > 0) or self.value_dim < 1:
+            raise ValueError(f"chunk {chunk!r}, softcap {softcap!r}, value_dim {value_dim!r}: positive numbers are needed")
+        self.value_mix, self.value_mix_key = value_mix, value_mix_key
+        # the kernels that fuse rotation and cache write take values as wide as the keys and plain causal scores
+        self.general = self.value_dim != self.head_dim or self.chunk is not None or self.softcap is not None or value_mix is not None
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
         self.window = None if window is None else int(window)
         self.scale = 1.0 / math.sqrt(self.head_dim) if scale is None else float(scale)
         self.position = POSITION_ENCODINGS.build(position) if position is not None else None
         self.names = {
             "q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-            "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", **(names or {}),
+            "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "value_mix": "vmix", **(names or {}),
         }
-        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.mix_weight = None
 
     # -- weights -------------------------------------------------------------------------
     def tensors(self) -> Sequence[TensorDecl]:
@@ -56,9 +79,11 @@ class GroupedQueryAttention(Mixer):
         decls = [
             TensorDecl(n["q"], (self.q_size, self.width)),
             TensorDecl(n["k"], (self.kv_size, self.width)),
-            TensorDecl(n["v"], (self.kv_size, self.width)),
-            TensorDecl(n["o"], (self.width, self.q_size)),
+            TensorDecl(n["v"], (self.v_size, self.width)),
+            TensorDecl(n["o"], (self.width, self.out_size)),
         ]
+        if self.value_mix is not None:   # the source layer's weight is in the checkpoint too, and is not used
+            decls.append(TensorDecl(n["value_mix"], (), "vector", (0.5, 0.1)))
         if self.qk_norm_eps is not None:
             decls += [TensorDecl(n["q_norm"], (self.head_dim,), "vector"), TensorDecl(n["k_norm"], (self.head_dim,), "vector")]
         return decls
@@ -70,16 +95,21 @@ class GroupedQueryAttention(Mixer):
         self.w_o = tensors[n["o"]].contiguous()
         if self.qk_norm_eps is not None:
             self.q_norm, self.k_norm = tensors[n["q_norm"]].contiguous(), tensors[n["k_norm"]].contiguous()
+        if self.value_mix == "mix":
+            self.mix_weight = tensors[n["value_mix"]].reshape(1).contiguous()
 
     def weight_bytes(self) -> int:
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size() + (0 if self.q_norm is None else 8 * self.head_dim)
 
     # -- cache ---------------------------------------------------------------------------
     def cache_need(self) -> CacheNeed:
-        return CacheNeed(kv=KVNeed(self.n_kv_heads, self.head_dim, self.window))
+        value_dim = None if self.value_dim == self.head_dim else self.value_dim
+        return CacheNeed(kv=KVNeed(self.n_kv_heads, self.head_dim, self.window, value_dim, self.chunk))
 
     # -- run -----------------------------------------------------------------------------
     def forward(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
+        if self.general:
+            return self._forward_general(h, step, cache)
         table = self.position.rotary_table(h.device) if self.position is not None else None
         cos, sin, rotary_dim = table if table is not None else (None, None, 0)
         q_norm, k_norm = self.q_norm, self.k_norm
@@ -109,5 +139,28 @@ class GroupedQueryAttention(Mixer):
             q, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
             self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale, row_tokens=step.row_tokens,
             rows_alike=step.rows_alike,
+        )
+        return ops.linear_for_residual(context, self.w_o)
+
+    def _forward_general(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
+        """Values of their own width, value mixing, chunks or a soft cap: the product, one kernel for norms, mixing and
+        cache write, attention, the output product."""
+        if self.position is not None:
+            raise NotImplementedError("a position encoding together with value_dim, chunk, softcap or value_mix is not built")
+        qkv = ops.linear(h, self.w_qkv)
+        other = step.carry.get(self.value_mix_key) if self.value_mix == "mix" else None
+        if self.value_mix == "mix" and other is None:
+            raise RuntimeError(f"no earlier layer of this step left values under {self.value_mix_key!r}")
+        ops.qk_norm_mix_kv_write(
+            qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, step.positions, step.token_row, cache.block_table, cache.page_size,
+            cache.k_pages, cache.v_pages, self.n_heads, self.n_kv_heads, self.head_dim, self.value_dim,
+            other_values=other, mix_weight=self.mix_weight if other is not None else None,
+        )
+        if self.value_mix == "source":
+            step.carry[self.value_mix_key] = qkv[:, self.q_size + self.kv_size:]
+        context = ops.paged_attention(
+            qkv, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
+            self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale, row_tokens=step.row_tokens,
+            rows_alike=step.rows_alike, chunk=self.chunk, softcap=self.softcap,
         )
         return ops.linear_for_residual(context, self.w_o)

@@ -38,12 +38,15 @@ class TensorDecl:
 
     ``role`` decides how it is held on the device: ``matrix`` in the compute dtype
     (bfloat16 or float32), ``vector`` (norm weights and the like, used in 32-bit math)
-    always in float32, ``table`` (integer tables) in int32.
+    always in float32, ``table`` (integer tables) in int32.  ``init``: (mean, standard deviation)
+    for the random-weights mode where the role's default (matrices N(0, 0.02), vectors
+    1 + N(0, 0.02)) would make a degenerate model, e.g. a mixing weight that must lie inside (0, 1).
     """
 
     name: str
     shape: tuple[int, ...]
     role: str = "matrix"
+    init: Optional[tuple[float, float]] = None
 
 
 # ---------------------------------------------------------------------------------------
@@ -57,13 +60,36 @@ class KVNeed:
     that width and no values).
 
     ``window``: a query at position p reads keys at positions (p - window, p]; ``None``
-    reads all of them.  Layers whose KVNeed is equal share a page pool (a cache group).
+    reads all of them.  ``chunk``: a query at position p reads only keys of its own chunk of
+    positions, ``[p - p % chunk, p]``.  Either lets the manager give pages back that no later
+    token can read.  Layers whose KVNeed is equal share a page pool (a cache group).
     """
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     value_dim: Optional[int] = None
+    chunk: Optional[int] = None
+
+    @property
+    def bounded(self) -> bool:
+        """Whether a token reads only a bounded span of positions before it, however long the request."""
+        return self.window is not None or self.chunk is not None
+
+    @property
+    def reach(self) -> Optional[int]:
+        """The most positions a token reads, itself included (``None``: all of them)."""
+        spans = [span for span in (self.window, self.chunk) if span is not None]
+        return min(spans) if spans else None
+
+    def first_needed(self, length: int) -> int:
+        """The oldest position that the token at position ``length``, or any later one, can read."""
+        first = 0
+        if self.window is not None:
+            first = max(first, length - self.window + 1)
+        if self.chunk is not None:
+            first = max(first, length - length % self.chunk)
+        return first
 
     @property
     def value_width(self) -> int:
@@ -124,6 +150,8 @@ class StepView:
     0.  Whatever a part computes for a padding token is never read; it must keep nothing of it
     (no cache write, no state update).  Only models whose parts all say ``takes_padding`` get
     such steps.
+    carry: what a part leaves for later parts of the same step, by a name the model's description chooses (the values
+    of one layer that later layers mix into their own, say).  Empty at the start of every step.
     """
 
     token_ids: torch.Tensor
@@ -143,6 +171,9 @@ class StepView:
     row_tokens: Optional[tuple] = None
     rows_alike: bool = False
     padded: bool = False
+
+    def __init__(self) -> None:
+        self.carry: dict = {}
 
 
 # ---------------------------------------------------------------------------------------
@@ -164,7 +195,10 @@ class Part:
 
 
 class Norm(Part):
-    def apply(self, stream: "ResidualStream", rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def apply(self, stream: "ResidualStream", rows: Optional[torch.Tensor] = None, read: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Fold what is pending into the stream and return the normalised activations of all tokens, or of ``rows``
+        only.  ``read``: for a stream of several copies, the float32 weights ``[copies]`` of the combination that is
+        normalised (``None``: their plain sum)."""
         raise NotImplementedError
 
 
@@ -217,30 +251,64 @@ class Block(Part):
         raise NotImplementedError
 
 
-class ResidualStream:
-    """The residual sum in float32 ``[T, width]`` plus the delta not yet added to it.
+@dataclass(frozen=True)
+class StreamRoute:
+    """How a sublayer's output goes back into a residual stream of several copies, all copies at once from the old ones:
+    ``x_t = sum_s mix[s, t] * x_s + scale * out[t] * y``.  ``mix`` float32 ``[copies, copies]`` indexed [from, to],
+    ``out`` float32 ``[copies]``, both on the device."""
 
-    Parts hand their output to ``add``; the next norm folds it in (one fused kernel reads
-    the delta once, updates the 32-bit sum and writes the normalised activations).  A delta
-    is ``[T, width]`` in the activation dtype, or float32 partial sums ``[parts, T, width]``
-    whose sum is the delta (what :func:`pylon_b200.kernels.ops.linear_for_residual` may return).
+    mix: torch.Tensor
+    out: torch.Tensor
+
+
+class ResidualStream:
+    """The residual sum in float32 plus the delta not yet added to it.
+
+    ``residual`` is ``[T, width]``, or ``[T, copies, width]`` for a model that keeps several copies of the stream
+    (hyper-connections).  Parts hand their output to ``add``; the next norm folds it in (one fused kernel reads the
+    delta once, updates the 32-bit sum and writes the normalised activations).  A delta is ``[T, width]`` in the
+    activation dtype, or float32 partial sums ``[parts, T, width]`` whose sum is the delta (what
+    :func:`pylon_b200.kernels.ops.linear_for_residual` may return).  ``add`` may name a factor on the delta and, for
+    several copies, the :class:`StreamRoute` by which it enters them.
     """
 
     def __init__(self, residual: torch.Tensor) -> None:
         self.residual = residual
         self.pending: Optional[torch.Tensor] = None
+        self.pending_scale = 1.0
+        self.pending_route: Optional[StreamRoute] = None
 
-    def add(self, delta: torch.Tensor) -> None:
+    @property
+    def plain(self) -> bool:
+        """One copy, and what is pending is added as it is: the case the fused add + RMSNorm kernels are written for."""
+        return self.residual.dim() == 2 and self.pending_scale == 1.0 and self.pending_route is None
+
+    def add(self, delta: torch.Tensor, scale: float = 1.0, route: Optional[StreamRoute] = None) -> None:
         if self.pending is not None:
             self.flush()
-        self.pending = delta
+        self.pending, self.pending_scale, self.pending_route = delta, float(scale), route
+
+    def take_pending(self) -> tuple[Optional[torch.Tensor], float, Optional[StreamRoute]]:
+        pending = (self.pending, self.pending_scale, self.pending_route)
+        self.pending, self.pending_scale, self.pending_route = None, 1.0, None
+        return pending
 
     def flush(self) -> None:
-        if self.pending is not None:
-            from pylon_b200.kernels import ops
+        if self.pending is None:
+            return
+        from pylon_b200.kernels import ops
 
+        if self.plain:
             ops.residual_add(self.residual, self.pending)
             self.pending = None
+            return
+        delta, scale, route = self.take_pending()
+        ops.streams_update_norm(self.residual, delta, scale, None if route is None else route.mix, None if route is None else route.out)
+
+    def total(self) -> torch.Tensor:
+        """The stream as one ``[T, width]`` tensor: the sum of its copies, with nothing pending."""
+        self.flush()
+        return self.residual if self.residual.dim() == 2 else self.residual.sum(dim=1)
 
 
 # ---------------------------------------------------------------------------------------

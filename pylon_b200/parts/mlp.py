@@ -2,6 +2,9 @@
 
 raun6k/Pylon's ``FeedForward`` (src/pylon/model/layers.py:13-27); the stacked ``[gate; up]``
 layout is the one its loader builds (src/pylon/model/weights.py:65-67).
+
+``clamped_glu`` is the same arrangement with another gated unit: ``g = min(gate(x), limit)``,
+``u = clamp(up(x), -limit, limit)``, ``down(g * sigmoid(alpha * g) * (u + 1))``.
 """
 from __future__ import annotations
 
@@ -15,8 +18,12 @@ from pylon_b200.parts.base import FEED_FORWARDS, FeedForward, StepView, TensorDe
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
-    def __init__(self, width: int, intermediate: int, names: Optional[Mapping[str, str]] = None) -> None:
+    def __init__(self, width: int, intermediate: int, names: Optional[Mapping[str, str]] = None,
+                 limit: Optional[float] = None, alpha: float = 1.0) -> None:
         self.width, self.intermediate = int(width), int(intermediate)
+        self.limit, self.alpha = (None if limit is None else float(limit)), float(alpha)
+        if self.limit is not None and not self.limit > 0:
+            raise ValueError(f"the limit of a clamped gated unit must be positive, got {limit!r}")
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
         self.w_gate_up = self.w_down = None
         self.interleaved = False
@@ -33,7 +40,7 @@ class SwiGLU(FeedForward):
         n = self.names
         # gate and up share one product.  In bfloat16 their rows alternate in groups of 8, so that
         # the product's kernel can apply silu(gate) * up itself; otherwise they lie in two halves.
-        self.interleaved = dtype == torch.bfloat16 and self.intermediate % 8 == 0
+        self.interleaved = dtype == torch.bfloat16 and self.intermediate % 8 == 0 and self.limit is None
         if self.interleaved:
             self.w_gate_up = ops.interleave_gate_up(tensors[n["gate"]], tensors[n["up"]])
         else:
@@ -47,5 +54,13 @@ class SwiGLU(FeedForward):
         if self.interleaved:
             activation = ops.linear_swiglu(h, self.w_gate_up)
         else:
-            activation = ops.swiglu(ops.linear(h, self.w_gate_up))
+            activation = ops.swiglu(ops.linear(h, self.w_gate_up), limit=self.limit, alpha=self.alpha)
         return ops.linear_for_residual(activation, self.w_down)
+
+
+@FEED_FORWARDS.register("clamped_glu")
+class ClampedGLU(SwiGLU):
+    """``down(g * sigmoid(alpha * g) * (u + 1))`` with ``g = min(gate(x), limit)`` and ``u = clamp(up(x), -limit, limit)``."""
+
+    def __init__(self, width: int, intermediate: int, limit: float, alpha: float = 1.702, names: Optional[Mapping[str, str]] = None) -> None:
+        super().__init__(width, intermediate, names, limit=limit, alpha=alpha)

@@ -33,7 +33,48 @@ class RMSNorm(Norm):
     def weight_bytes(self) -> int:
         return self.width * 4
 
-    def apply(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def apply(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, read: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if not stream.plain:
+            return _apply_to_streams(self, "rmsnorm", stream, rows, read)
         delta, stream.pending = stream.pending, None
         # With a row selection the residual stays untouched and the delta is added on the fly.
         return ops.add_rmsnorm(stream.residual, delta, self.weight, self.eps, self.dtype, rows=rows)
+
+
+def _apply_to_streams(norm, kind: str, stream: ResidualStream, rows: Optional[torch.Tensor], read: Optional[torch.Tensor]) -> torch.Tensor:
+    """The general form: one or several copies of the stream, a factor on the pending delta, a route by which it enters
+    the copies, the combination of copies that is read, layer norm or RMS norm - one kernel."""
+    if rows is None:
+        delta, scale, route = stream.take_pending()
+    else:   # the stream stays as it is: what is pending stays pending
+        delta, scale, route = stream.pending, stream.pending_scale, stream.pending_route
+    return ops.streams_update_norm(
+        stream.residual, delta, scale, None if route is None else route.mix, None if route is None else route.out, read,
+        norm.weight, norm.eps, kind, norm.dtype, rows=rows,
+    )
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * weight`` in float32, the variance being the mean of the squared deviations;
+    a weight and no bias.  Like :class:`RMSNorm` it is where a pending delta joins the residual stream."""
+
+    def __init__(self, width: int, eps: float, weight_name: str = "weight") -> None:
+        self.width = int(width)
+        self.eps = float(eps)
+        self.weight_name = weight_name
+        self.weight: Optional[torch.Tensor] = None
+        self.dtype: Optional[torch.dtype] = None
+
+    def tensors(self) -> Sequence[TensorDecl]:
+        return (TensorDecl(self.weight_name, (self.width,), "vector"),)
+
+    def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
+        self.weight = tensors[self.weight_name].contiguous()
+        self.dtype = dtype
+
+    def weight_bytes(self) -> int:
+        return self.width * 4
+
+    def apply(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, read: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return _apply_to_streams(self, "layernorm", stream, rows, read)

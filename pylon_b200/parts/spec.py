@@ -65,6 +65,7 @@ class ModelSpec:
     embedding_scale: float = 1.0            # the embedding rows are multiplied by it as they enter the residual stream
     logit_scale: float = 1.0                # the logits are multiplied by it,
     logit_softcap: Optional[float] = None   # then, with a cap c, squashed to c * tanh(logit / c)
+    streams: int = 1                        # copies of the residual stream (hyper-connections); all start as the embedding row
 
     def __post_init__(self) -> None:
         runs = tuple(run if isinstance(run, RunSpec) else RunSpec(int(run)) for run in self.order)

@@ -22,9 +22,11 @@ from pylon_b200.models.decoder import DecoderModel
 _STORE_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
-def random_tensor(name: str, shape: tuple[int, ...], role: str, seed: int) -> torch.Tensor:
+def random_tensor(name: str, shape: tuple[int, ...], role: str, seed: int, init=None) -> torch.Tensor:
     generator = torch.Generator(device="cpu")
     generator.manual_seed((int(seed) * 1_000_003 + zlib.crc32(name.encode())) % (2**63 - 1))
+    if init is not None:   # (mean, standard deviation) that the part asks for
+        return torch.randn(shape, generator=generator, dtype=torch.float32) * float(init[1]) + float(init[0])
     values = torch.randn(shape, generator=generator, dtype=torch.float32) * 0.02
     return values + 1.0 if role == "vector" else values
 
@@ -39,7 +41,7 @@ def write_random_model(config: Any, seed: int, folder: str | Path, dtype: str = 
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
     tensors = {
-        name: random_tensor(name, decl.shape, decl.role, seed).to(_STORE_DTYPES[dtype]).contiguous()
+        name: random_tensor(name, decl.shape, decl.role, seed, decl.init).to(_STORE_DTYPES[dtype]).contiguous()
         for name, decl in model.tensor_decls().items()
     }
     save_file(tensors, str(folder / "model.safetensors"), metadata={"format": "pt"})
@@ -60,6 +62,8 @@ def device_random_fetch(decls, seed: int, device: torch.device, dtype: torch.dty
         generator.manual_seed((int(seed) * 1_000_003 + zlib.crc32(name.encode())) % (2**63 - 1))
         target = torch.float32 if decl.role == "vector" else dtype
         values = torch.empty(decl.shape, dtype=target, device=device)
+        if decl.init is not None:
+            return values.normal_(float(decl.init[0]), float(decl.init[1]), generator=generator)
         values.normal_(0.0, 0.02, generator=generator)
         return values + 1.0 if decl.role == "vector" else values
 

@@ -64,8 +64,31 @@ def clamped_glu(h: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: tor
 # ---------------------------------------------------------------------------------------
 # attention in chunks of positions, scores soft-capped, values mixed with an earlier layer's
 # ---------------------------------------------------------------------------------------
-def visible(i: int, j: int, chunk: Optional[int]) -> bool:
-    return j <= i and (chunk is None or i // chunk == j // chunk)
+def visible(count: int, chunk: Optional[int]) -> torch.Tensor:
+    """``[i, j]`` true where position i sees position j: j <= i, and in the same chunk of positions if there are chunks."""
+    i = torch.arange(count)[:, None]
+    j = torch.arange(count)[None, :]
+    seen = j <= i
+    if chunk is not None:
+        seen = seen & (torch.div(i, chunk, rounding_mode="floor") == torch.div(j, chunk, rounding_mode="floor"))
+    return seen
+
+
+def attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, softcap: Optional[float],
+                   chunk: Optional[int]) -> torch.Tensor:
+    """``q [T, heads, dim]``, ``k [T, kv_heads, dim]``, ``v [T, kv_heads, vdim]`` of one sequence -> ``[T, heads, vdim]``."""
+    count, heads = q.shape[0], q.shape[1]
+    group = heads // k.shape[1]
+    seen = visible(count, chunk)
+    out = torch.zeros(count, heads, v.shape[2], dtype=q.dtype)
+    for head in range(heads):
+        kv = head // group
+        scores = (q[:, head] @ k[:, kv].T) * scale
+        if softcap:
+            scores = softcap * torch.tanh(scores / softcap)
+        scores = scores.masked_fill(~seen, float("-inf"))
+        out[:, head] = torch.softmax(scores, dim=-1) @ v[:, kv]
+    return out
 
 
 def chunked_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], p: Mapping, eps: float,
@@ -84,22 +107,33 @@ def chunked_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], p: Mapping
     if v_first is not None:
         lam = w["vmix"]
         v = (1 - lam) * v + lam * v_first
-    out = torch.zeros(count, heads, vdim, dtype=h.dtype)
-    for head in range(heads):
-        kv = head // (heads // kv_heads)
-        for i in range(count):
-            keys = [j for j in range(i + 1) if visible(i, j, chunk)]
-            scores = torch.stack([(q[i, head] * k[j, kv]).sum() for j in keys]) * p["scale"]
-            if p.get("softcap"):
-                scores = p["softcap"] * torch.tanh(scores / p["softcap"])
-            weights = torch.softmax(scores, dim=0)
-            out[i, head] = (weights[:, None] * v[keys, kv]).sum(dim=0)
+    out = attention_core(q, k, v, p["scale"], p.get("softcap"), chunk)
     return out.reshape(count, heads * vdim) @ w["o"].T, v
 
 
 # ---------------------------------------------------------------------------------------
 # gated delta rule
 # ---------------------------------------------------------------------------------------
+def delta_recurrence(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor,
+                     states: Optional[list] = None) -> torch.Tensor:
+    """``q, k [T, kv_heads, dim]``, ``v [T, heads, vdim]``, ``decay, beta [T, heads]`` -> read-outs ``[T, heads, vdim]``.
+    Per head: S = g S; w = beta (v - S^T k); S = S + k w^T; o = S^T q.  ``states`` (a list) receives the final S of each head."""
+    count, heads, vdim = v.shape
+    kv_heads, dim = k.shape[1], k.shape[2]
+    out = torch.zeros(count, heads, vdim, dtype=v.dtype)
+    for head in range(heads):
+        kv = head // (heads // kv_heads)
+        state = torch.zeros(dim, vdim, dtype=v.dtype)
+        for t in range(count):
+            state = decay[t, head] * state
+            write = beta[t, head] * (v[t, head] - state.T @ k[t, kv])
+            state = state + torch.outer(k[t, kv], write)
+            out[t, head] = state.T @ q[t, kv]
+        if states is not None:
+            states.append(state)
+    return out
+
+
 def gated_delta(h: torch.Tensor, w: Mapping[str, torch.Tensor], p: Mapping, eps: float) -> torch.Tensor:
     count = h.shape[0]
     heads, kv_heads, dim, vdim = p["heads"], p["kv_heads"], p["dim"], p["vdim"]
@@ -111,15 +145,7 @@ def gated_delta(h: torch.Tensor, w: Mapping[str, torch.Tensor], p: Mapping, eps:
     beta = torch.sigmoid(h @ w["b"].T)                                     # [T, heads]
     decay = torch.exp(-torch.exp(w["A_log"]) * softplus(h @ w["a"].T + w["dt_bias"]))
     gate = silu(h @ w["g"].T).view(count, heads, vdim)
-    out = torch.zeros(count, heads, vdim, dtype=h.dtype)
-    for head in range(heads):
-        kv = head // (heads // kv_heads)
-        state = torch.zeros(dim, vdim, dtype=h.dtype)
-        for t in range(count):
-            state = decay[t, head] * state
-            write = beta[t, head] * (v[t, head] - state.T @ k[t, kv])
-            state = state + torch.outer(k[t, kv], write)
-            out[t, head] = state.T @ q[t, kv]
+    out = delta_recurrence(q, k, v, decay, beta)
     out = rms_unit(out, eps) * w["norm"] * gate
     return out.reshape(count, heads * vdim) @ w["o"].T
 

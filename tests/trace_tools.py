@@ -168,7 +168,7 @@ def run_program(model_dir: Path, dtype: str, steps: Sequence[dict], out_dir: Pat
                 extra_args: Sequence[str] = (), env: Optional[dict] = None) -> dict[str, np.ndarray]:
     """Replays ``steps`` with the ``bin/trace_run`` program in a process of its own."""
     config = json.loads((Path(model_dir) / "config.json").read_text())
-    vocab = config["vocab_size"]
+    vocab = config["vocab_size"] if "vocab_size" in config else config["vocab"]
     max_tokens = pool_tokens(steps) if max_tokens is None else max_tokens
     command = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype,
                "--out", str(out_dir), "--max-tokens", str(max_tokens), *extra_args]

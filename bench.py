@@ -470,6 +470,179 @@ def run_serving_workload(name: str, torch) -> dict:
     }
 
 
+# ---------------------------------------------------------------------------------------
+# Vopepel beside Qwen3 at equal size (--workload designs)
+# ---------------------------------------------------------------------------------------
+DESIGN_SIZES = {
+    # width, layers, heads / kv heads / head size of the attention, inner width of the feed-forward, vocabulary
+    "2k": dict(width=2_048, layers=8, heads=16, kv_heads=4, head_dim=128, ff=8_192, vocab=32_768),
+    "4k": dict(width=4_096, layers=8, heads=32, kv_heads=8, head_dim=128, ff=12_288, vocab=32_768),
+}
+DESIGN_CONTEXT = 2_048
+_TIMED_OPS = ("linear", "linear_for_residual", "linear_swiglu", "linear_for_rotation", "linear_qkv_rotated", "paged_attention", "gated_delta_rule",
+              "streams_update_norm", "add_rmsnorm", "swiglu", "qk_norm_mix_kv_write", "qk_norm_rope_kv_write", "embed_gather")
+
+
+def vopepel_fields(size: dict) -> dict:
+    """A Vopepel model of the given size: of every four layers the first is a gated delta rule, the others attention in
+    chunks of 1,024 positions with value mixing; four copies of the residual stream."""
+    def layer(index: int) -> dict:
+        mlp = {"kind": "dense", "ff": size["ff"], "limit": 7.0}
+        if index % 4 == 0:
+            return {"type": "delta", "mlp": mlp, "mixer": {"heads": size["heads"], "kv_heads": size["heads"] // 2, "dim": size["head_dim"],
+                                                           "vdim": size["head_dim"], "conv": 4}}
+        return {"type": "attention", "mlp": mlp, "mixer": {"heads": size["heads"], "kv_heads": size["kv_heads"], "dim": size["head_dim"],
+                                                           "vdim": size["head_dim"], "scale": size["head_dim"] ** -0.5, "softcap": 30.0,
+                                                           "mask": {"size": 1_024}, "v_mix": True}}
+    return {"architecture": "Vopepel", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.5, "streams": 4,
+            "layers": [layer(index) for index in range(size["layers"])]}
+
+
+def qwen3_fields(size: dict) -> dict:
+    return dict(vocab_size=size["vocab"], hidden_size=size["width"], num_hidden_layers=size["layers"], num_attention_heads=size["heads"],
+                num_key_value_heads=size["kv_heads"], head_dim=size["head_dim"], intermediate_size=size["ff"], max_position_embeddings=32_768,
+                rope_theta=1_000_000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+
+
+class OpTimer:
+    """CUDA events around the calls of the engine's kernels entry points during a step, summed by entry point.  Only the
+    outermost call counts (an entry point that hands on to another is one call)."""
+
+    def __init__(self, ops, torch) -> None:
+        self.ops, self.torch, self.depth, self.records, self.saved = ops, torch, 0, [], {}
+
+    def __enter__(self):
+        for name in _TIMED_OPS:
+            original = getattr(self.ops, name)
+            self.saved[name] = original
+            setattr(self.ops, name, self._wrap(name, original))
+        return self
+
+    def _wrap(self, name, original):
+        def timed(*args, **kwargs):
+            if self.depth:
+                return original(*args, **kwargs)
+            begin, end = self.torch.cuda.Event(enable_timing=True), self.torch.cuda.Event(enable_timing=True)
+            self.depth += 1
+            begin.record()
+            try:
+                return original(*args, **kwargs)
+            finally:
+                end.record()
+                self.depth -= 1
+                self.records.append((name, begin, end))
+        return timed
+
+    def __exit__(self, *exc) -> None:
+        for name, original in self.saved.items():
+            setattr(self.ops, name, original)
+
+    def table(self) -> dict:
+        self.torch.cuda.synchronize()
+        total: dict = {}
+        for name, begin, end in self.records:
+            entry = total.setdefault(name, [0, 0.0])
+            entry[0] += 1
+            entry[1] += begin.elapsed_time(end) * 1e3
+        return {name: {"calls": calls, "us": round(us, 1)} for name, (calls, us) in sorted(total.items(), key=lambda item: -item[1][1])}
+
+
+def time_design(engine, torch, ops, rng, batch: int, steps: int) -> dict:
+    """Prefill of one 2,048-token prompt (best of three after two warm-up runs) and decode steps of ``batch`` requests that
+    hold about 2,048 tokens each (CUDA events around ``steps`` steps, after warm-up), with the time of each kernel entry point."""
+    from pylon_b200.engine import StepEntry
+
+    vocab = engine.spec.vocab_size
+    out: dict = {}
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    best = None
+    for index in range(6):
+        request = engine.open(("prefill", index), PREFILL_TOKENS)
+        tokens = rng.integers(0, vocab, size=PREFILL_TOKENS).tolist()
+        timer = OpTimer(ops, torch) if index == 5 else None
+        torch.cuda.synchronize()
+        begin.record()
+        if timer is not None:
+            with timer:
+                engine.step([StepEntry(request, tokens, (PREFILL_TOKENS - 1,))])
+        else:
+            engine.step([StepEntry(request, tokens, (PREFILL_TOKENS - 1,))])
+        end.record()
+        torch.cuda.synchronize()
+        engine.close(request)
+        if 2 <= index < 5:
+            best = begin.elapsed_time(end) if best is None else min(best, begin.elapsed_time(end))
+        if timer is not None:
+            out["prefill_kernels_us"] = timer.table()
+    out["prefill_ms"] = round(best, 3)
+    out["prefill_tokens_per_second"] = round(PREFILL_TOKENS / (best / 1e3), 1)
+    requests = fill_caches(engine, torch, batch, DESIGN_CONTEXT - steps - 12, rng, PREFILL_TOKENS)
+    tokens = rng.integers(0, vocab, size=batch).tolist()
+    loop = DecodeLoop(engine, requests, tokens)
+    for _ in range(8):
+        loop.step()
+    loop.finish()
+    torch.cuda.synchronize()
+    before = ops.launches[0]
+    begin.record()
+    for _ in range(steps):
+        loop.step()
+    loop.finish()
+    end.record()
+    torch.cuda.synchronize()
+    out["decode_launches_per_step"] = (ops.launches[0] - before) / steps
+    milliseconds = begin.elapsed_time(end) / steps
+    out["decode_ms_per_step"] = round(milliseconds, 4)
+    out["decode_tokens_per_second"] = round(batch / (milliseconds / 1e3), 1)
+    graphs, engine.step_function.graphs = engine.step_function.graphs, None     # one eager step under the timer
+    try:
+        with OpTimer(ops, torch) as timer:
+            engine.step([StepEntry(request, [1], (0,)) for request in requests])
+        out["decode_kernels_us"] = timer.table()
+    finally:
+        engine.step_function.graphs = graphs
+    weight_bytes = engine.model.weight_bytes()
+    kv_bytes = batch * DESIGN_CONTEXT * engine.cache.bytes_per_token() + batch * engine.cache.state_bytes_per_request() * 2
+    out["decode_bytes_per_step"] = int(weight_bytes + kv_bytes)
+    for request in requests:
+        engine.close(request)
+    return out
+
+
+def run_design_comparison(torch, sizes, batch: int, steps: int) -> dict:
+    """Vopepel and Qwen3 dense at equal width, depth, heads, feed-forward and vocabulary: prefill and decode throughput and
+    the time of every kernel entry point, random weights."""
+    import gc
+
+    import numpy as np
+
+    from pylon_b200.config import EngineConfig, Qwen3Config
+    from pylon_b200.config.model_config import VopepelConfig
+    from pylon_b200.engine import Engine
+    from pylon_b200.kernels import ops
+
+    peak = peaks()
+    record = {"metric": "prefill and decode, Vopepel beside Qwen3 at equal size", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+              "data": "synthetic: random weights, uniform random token ids, caches filled by real prefill",
+              "config": {"prefill_tokens": PREFILL_TOKENS, "decode_batch": batch, "decode_context": DESIGN_CONTEXT, "decode_steps": steps,
+                         "page_size": PAGE_SIZE, "cuda_graphs": True, "peaks": peak["source"]}, "sizes": {}}
+    for name in sizes:
+        size = DESIGN_SIZES[name]
+        entry = {"size": size}
+        for design, model_config in (("vopepel", VopepelConfig.from_dict(vopepel_fields(size))), ("qwen3", Qwen3Config(**qwen3_fields(size)))):
+            config = EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=(batch + 1) * DESIGN_CONTEXT, max_context=DESIGN_CONTEXT,
+                                  max_batch_size=batch + 1, prefill_chunk_size=PREFILL_TOKENS, cuda_graphs=True)
+            engine = Engine(None, config, device="cuda:0", model_config=model_config, random_seed=0)
+            result = time_design(engine, torch, ops, np.random.default_rng(0), batch, steps)
+            result["decode_hbm_frac"] = round(result["decode_bytes_per_step"] / (result["decode_ms_per_step"] / 1e3) / 1e9 / peak["hbm_gbs"], 4)
+            entry[design] = result
+            del engine
+            gc.collect()
+            torch.cuda.empty_cache()
+        record["sizes"][name] = entry
+    return record
+
+
 def prefill_flops(cfg: dict, tokens: int) -> float:
     h, q, kv, inter = cfg["hidden_size"], cfg["num_attention_heads"] * cfg["head_dim"], cfg["num_key_value_heads"] * cfg["head_dim"], cfg["intermediate_size"]
     per_layer = 2 * tokens * (h * (q + 2 * kv) + q * h + 3 * h * inter)
@@ -523,8 +696,10 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=QWEN3_4B["num_hidden_layers"],
                         help="run fewer layers than the configuration has (named in the output)")
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
-    parser.add_argument("--workload", choices=["decode4b", "mixed8b", "sampled14b"], default="decode4b",
-                        help="decode4b: the headline measurement (default); the others are the serving workloads of the 8B and 14B shapes")
+    parser.add_argument("--workload", choices=["decode4b", "mixed8b", "sampled14b", "designs"], default="decode4b",
+                        help="decode4b: the headline measurement (default); mixed8b, sampled14b: the serving workloads of the 8B and 14B shapes; "
+                             "designs: Vopepel beside Qwen3 at equal size, prefill and decode with the time of every kernel entry point")
+    parser.add_argument("--design-sizes", default="2k,4k", help="with --workload designs: which of the sizes 2k, 4k")
     parser.add_argument("--profile", choices=["decode", "prefill"],
                         help="no measurement: run a few steps of this kind between cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     parser.add_argument("--profile-tokens", type=int, default=PREFILL_TOKENS, help="with --profile prefill: tokens of the prompt")
@@ -546,6 +721,9 @@ def main() -> int:
     from pylon_b200.engine import Engine
     from pylon_b200.kernels import ops
 
+    if args.workload == "designs":
+        print(json.dumps(run_design_comparison(torch, [name for name in args.design_sizes.split(",") if name], args.batch, min(args.steps, 32))))
+        return 0
     if args.workload != "decode4b":
         print(json.dumps(run_serving_workload(args.workload, torch)))
         return 0

@@ -49,12 +49,22 @@ struct AttentionParams {
   const int* kv_len;
   const int* block_table;
   int table_width, page_size, num_pages, nq, nkv, group, window, num_splits, total_tokens, num_rows;
+  int chunk;            // > 0: a token sees only keys of its own chunk of positions, [pos - pos % chunk, pos]
+  float cap_pre;        // > 0: a soft cap c on the scaled scores; the raw score s becomes tanh(s * cap_pre), cap_pre = scale / c,
+                        // and scale_log2 is c * log2(e), so that the softmax is that of c * tanh(scale * s / c)
   int small_rows_elsewhere;   // rows of at most SMALL_ROWS packed query rows are left to the decode kernel
   int incoming_rows;          // the cluster form's buffers for partial results hold this many packed query rows
   unsigned* counters;         // [rows * nkv], zero between launches: the last block of a decoded (row, KV head) combines its segments
   int* error;                 // set non-zero when a bounded wait for a TMA copy ran out (the output is then void)
   float scale_log2;     // softmax scale * log2(e)
 };
+
+// The first key that the token at position pos sees (a window, a chunk of positions, both or neither); it never decreases with pos.
+__device__ __forceinline__ int first_visible(const AttentionParams& p, int pos) {
+  int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  if (p.chunk > 0) lo = max(lo, pos - pos % p.chunk);
+  return lo;
+}
 
 constexpr int SMALL_ROWS = 16;   // packed query rows (tokens x group) one MMA tile holds
 
@@ -87,6 +97,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
+}
+// tanh to float32 accuracy from one exponential and one division: 1 - 2 / (e^(2x) + 1); +-1 at the ends (e^(2x) = inf or 0).
+__device__ __forceinline__ float soft_tanh(float x) {
+  const float e = fast_exp2(x * 2.8853900817779268f);
+  return 1.f - __fdividef(2.f, e + 1.f);
 }
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -160,7 +175,7 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const 
   const int last_packed = min(packed_rows, m0 + BM) - 1;
   const int token_last = last_packed / G;
   const int hi = pos0 + token_last;                                                   // last visible key (inclusive)
-  const int lo = p.window > 0 ? max(0, pos0 + token_first - p.window + 1) : 0;        // first visible key
+  const int lo = first_visible(p, pos0 + token_first);                                // first visible key
   const int first_tile = lo / BLOCK_N, tiles = hi / BLOCK_N - first_tile + 1;
   const int per_split = (tiles + p.num_splits - 1) / p.num_splits;
   const int tile_begin = first_tile + split * per_split;
@@ -168,7 +183,8 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const 
   const bool contiguous = p.page_size % BLOCK_N == 0;
 
   // This thread's rows: two per MMA tile.  Packed index, token position, validity.
-  int row_pos[MT][2], row_token[MT][2], row_head[MT][2];
+  int row_pos[MT][2], row_token[MT][2], row_head[MT][2], row_lo[MT][2];
+  const bool bounded = p.window > 0 || p.chunk > 0;
   bool row_valid[MT][2];
   int warp_min_pos = 0x7fffffff;
 #pragma unroll
@@ -180,6 +196,7 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const 
       row_token[mt][h] = row_valid[mt][h] ? m / G : 0;
       row_head[mt][h] = kv_head * G + (row_valid[mt][h] ? m % G : 0);
       row_pos[mt][h] = pos0 + row_token[mt][h];
+      row_lo[mt][h] = first_visible(p, row_pos[mt][h]);
     }
   }
   // Smallest position among the warp's rows (rows past the end count as the first row): tiles
@@ -263,7 +280,15 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const 
         // Mask: key visible iff key <= position (and > position - window) and the row exists.
         // A tile wholly at or below every row's position (and inside every window) needs none.
         const int tile_last_key = tile * BLOCK_N + BLOCK_N - 1;
-        const bool no_mask = warp_full && tile_last_key <= warp_min_pos && p.window == 0;
+        const bool no_mask = warp_full && tile_last_key <= warp_min_pos && !bounded;
+        if (p.cap_pre > 0.f) {
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int n = 0; n < BLOCK_N / 8; ++n)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) s[mt][n][i] = soft_tanh(s[mt][n][i] * p.cap_pre);
+        }
         if (!no_mask) {
           const int key_base = tile * BLOCK_N + 2 * tq;
 #pragma unroll
@@ -274,8 +299,7 @@ __global__ void __launch_bounds__(ATT_THREADS) paged_attention_mma_kernel(const 
               for (int i = 0; i < 4; ++i) {
                 const int h = i >> 1;
                 const int key = key_base + n * 8 + (i & 1);
-                bool visible = row_valid[mt][h] && key <= row_pos[mt][h];
-                if (p.window > 0) visible = visible && key > row_pos[mt][h] - p.window;
+                const bool visible = row_valid[mt][h] && key <= row_pos[mt][h] && key >= row_lo[mt][h];
                 if (!visible) s[mt][n][i] = -INFINITY;
               }
             }
@@ -472,7 +496,7 @@ __device__ __forceinline__ int decode_row_tiles(const AttentionParams& p, int ro
   if (packed_rows <= 0 || packed_rows > SMALL_ROWS) return 0;
   const int pos0 = p.kv_len[row] - q_len;
   const int hi = pos0 + q_len - 1;
-  const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int lo = first_visible(p, pos0);
   if (hi < lo) return 0;
   *first_tile = lo / BLOCK_N;
   return hi / BLOCK_N - lo / BLOCK_N + 1;
@@ -765,13 +789,14 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ?
     const int kv_len = current.kv_len, pos0 = current.pos0;
     int issued_ahead = 0;   // tiles of this segment asked for before the wait for the kernel ahead (first segment only)
 
-    int row_pos[2];
+    int row_pos[2], row_lo[2];
     bool row_valid[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int m = g + 8 * h;
       row_valid[h] = m < packed_rows;
       row_pos[h] = pos0 + (row_valid[h] ? m / G : 0);
+      row_lo[h] = first_visible(p, row_pos[h]);
     }
 
     float o[D / 8][4];
@@ -879,7 +904,13 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ?
 #pragma unroll
         for (int i = 0; i < 4; ++i) s[n][i] += s_odd[n][i];
       // Tiles that end at or before the row's first new token, with no window, are visible whole.
-      if (p.window > 0 || tile * BLOCK_N + BLOCK_N - 1 > pos0) {
+      if (p.cap_pre > 0.f) {
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) s[n][i] = soft_tanh(s[n][i] * p.cap_pre);
+      }
+      if (p.window > 0 || p.chunk > 0 || tile * BLOCK_N + BLOCK_N - 1 > pos0) {
         const int key_base = tile * BLOCK_N + warp * 16 + 2 * tq;
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
@@ -887,8 +918,7 @@ __global__ void __launch_bounds__(ATT_THREADS, D <= 128 && CLUSTER_STAGES <= 2 ?
           for (int i = 0; i < 4; ++i) {
             const int h = i >> 1;
             const int key = key_base + n * 8 + (i & 1);
-            bool visible = row_valid[h] && key <= row_pos[h];
-            if (p.window > 0) visible = visible && key > row_pos[h] - p.window;
+            const bool visible = row_valid[h] && key <= row_pos[h] && key >= row_lo[h];
             if (!visible) s[n][i] = -INFINITY;
           }
         }
@@ -1279,13 +1309,15 @@ extern "C" long long pylon_attention_scratch_floats(int num_splits, int total_to
 // the rows of decoded tokens hold about equally many keys; with few of them, each (row, KV head) pair then gets a
 // thread-block cluster of its own (with rows of very different lengths that would leave most blocks idle: the result is
 // right either way).
-extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
-                                         void* out, float* scratch, unsigned* counters, const int* q_start, const int* kv_len,
-                                         const int* block_table, int table_width, int page_size, int num_pages,
-                                         int nq, int nkv, int window, float scale, int num_rows, int total_tokens,
-                                         int max_q, int num_splits, int decode_blocks, int skip_large, int rows_alike, int* error,
-                                         cudaStream_t stream) {
+// chunk > 0: attention inside chunks of positions (see AttentionParams); softcap c > 0: scaled scores go through c * tanh(s / c).
+extern "C" int pylon_paged_attention_mma_masked(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                                void* out, float* scratch, unsigned* counters, const int* q_start, const int* kv_len,
+                                                const int* block_table, int table_width, int page_size, int num_pages,
+                                                int nq, int nkv, int window, int chunk, float softcap, float scale, int num_rows,
+                                                int total_tokens, int max_q, int num_splits, int decode_blocks, int skip_large,
+                                                int rows_alike, int* error, cudaStream_t stream) {
   if (num_rows <= 0 || total_tokens <= 0) return 0;
+  if (chunk < 0 || softcap < 0.f) PYLON_REFUSE("paged_attention_mma: chunk %d, soft cap %f", chunk, softcap);
   if (nkv < 1 || nq < 1 || nq % nkv) PYLON_REFUSE("paged_attention_mma: %d query heads over %d KV heads", nq, nkv);
   if (page_size < 1 || table_width < 1 || window < 0 || max_q < 1 || num_splits < 1)
     PYLON_REFUSE("paged_attention_mma: page size %d, table width %d, window %d, longest row %d, splits %d", page_size,
@@ -1351,7 +1383,9 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
   p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
   p.nq = nq; p.nkv = nkv; p.group = group; p.window = window; p.num_splits = num_splits; p.total_tokens = total_tokens;
   p.num_rows = num_rows;
-  p.scale_log2 = scale * 1.4426950408889634f;
+  p.scale_log2 = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f;
+  p.chunk = chunk;
+  p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
   p.small_rows_elsewhere = maybe_small ? 1 : 0;
   p.incoming_rows = (int)(packed_max < SMALL_ROWS ? packed_max : SMALL_ROWS);
   if (run_tiled) {
@@ -1405,4 +1439,16 @@ extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, cons
                      maybe_small ? 1 : 0);
   }
   PYLON_CHECK_LAUNCH("paged_attention_mma");
+}
+
+// The same without chunks and soft cap.
+extern "C" int pylon_paged_attention_mma(const void* q, long long q_stride, const void* k_pages, const void* v_pages,
+                                         void* out, float* scratch, unsigned* counters, const int* q_start, const int* kv_len,
+                                         const int* block_table, int table_width, int page_size, int num_pages,
+                                         int nq, int nkv, int window, float scale, int num_rows, int total_tokens,
+                                         int max_q, int num_splits, int decode_blocks, int skip_large, int rows_alike, int* error,
+                                         cudaStream_t stream) {
+  return pylon_paged_attention_mma_masked(q, q_stride, k_pages, v_pages, out, scratch, counters, q_start, kv_len, block_table, table_width,
+                                          page_size, num_pages, nq, nkv, window, 0, 0.f, scale, num_rows, total_tokens, max_q, num_splits,
+                                          decode_blocks, skip_large, rows_alike, error, stream);
 }

@@ -69,9 +69,19 @@ struct FaParams {
   const int* kv_len;
   const int* block_table;
   int table_width, page_size, num_pages, nq, nkv, group, window, skip_small, first_row;
+  int chunk;          // > 0: a token sees only keys of its own chunk of positions, [pos - pos % chunk, pos]
+  float cap_pre;      // > 0: a soft cap c on the scaled scores: the raw score s becomes tanh(s * cap_pre), cap_pre = scale / c, and
+                      // scale_log2 is c * log2(e), so that the softmax is that of c * tanh(scale * s / c)
   float scale_log2;
   int* error;
 };
+
+// The first key that the token at position pos sees (a window, a chunk of positions, both or neither); it never decreases with pos.
+__device__ __forceinline__ int fa_first_visible(const FaParams& p, int pos) {
+  int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+  if (p.chunk > 0) lo = max(lo, pos - pos % p.chunk);
+  return lo;
+}
 
 __device__ __forceinline__ unsigned fa_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void fa_mbar_init(uint64_t* bar, int count) {
@@ -226,7 +236,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
   const int* table = p.block_table + (size_t)row * p.table_width;
   const int token_lo = m0 / G, token_hi = min(q_len - 1, (m0 + FA_BM - 1) / G);
   const int key_hi = pos0 + token_hi;
-  const int key_lo = p.window > 0 ? max(0, pos0 + token_lo - p.window + 1) : 0;
+  const int key_lo = fa_first_visible(p, pos0 + token_lo);
   const int first_tile = key_lo / FA_BN, num_tiles = key_hi / FA_BN - first_tile + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -339,6 +349,7 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
     const int token = valid ? m / G : 0;
     const int head = kv_head * G + (valid ? m % G : 0);
     const int pos = pos0 + token;
+    const int first_seen = fa_first_visible(p, pos);
     // The query row, in the layout the tensor core reads: 128-byte rows, 16-byte unit u of row r at u ^ (r % 8).
     {
       const uint4* src = reinterpret_cast<const uint4*>(p.q + (size_t)(q0 + token) * p.q_stride + (size_t)head * D);
@@ -369,12 +380,16 @@ __global__ void __launch_bounds__(FA_THREADS, 2) attention_tcgen05_kernel(const 
       }
       const int key0 = (first_tile + t) * FA_BN;
       // Tiles that end at or before the block's first token, with no window and only valid rows, are visible whole.
-      if (p.window > 0 || key0 + FA_BN - 1 > pos0 + token_lo || !valid) {
+      if (p.cap_pre > 0.f) {
+        // tanh to float32 accuracy from one exponential and one division: 1 - 2 / (e^(2x) + 1)
+#pragma unroll
+        for (int j = 0; j < FA_BN; ++j) s[j] = 1.f - __fdividef(2.f, fa_exp2(s[j] * (p.cap_pre * 2.8853900817779268f)) + 1.f);
+      }
+      if (p.window > 0 || p.chunk > 0 || key0 + FA_BN - 1 > pos0 + token_lo || !valid) {
 #pragma unroll
         for (int j = 0; j < FA_BN; ++j) {
           const int key = key0 + j;
-          bool visible = valid && key <= pos;
-          if (p.window > 0) visible = visible && key > pos - p.window;
+          const bool visible = valid && key <= pos && key >= first_seen;
           if (!visible) s[j] = -INFINITY;
         }
       }
@@ -521,11 +536,14 @@ extern "C" int pylon_attention_tcgen05_head_dim() { return D; }
 // which rows bring prompt portions names just those); max_q: the longest row (or an upper bound).  skip_small != 0: rows
 // with at most 16 packed query rows (tokens x group) are left alone (another kernel writes them).  error: one int in device memory that the kernel sets
 // non-zero when one of its bounded waits ran out (the output is then void).
-extern "C" int pylon_paged_attention_tcgen05(const void* q, long long q_stride, const void* k_pages, const void* v_pages, void* out,
-                                             const int* q_start, const int* kv_len, const int* block_table, int table_width,
-                                             int page_size, int num_pages, int nq, int nkv, int window, float scale, int first_row,
-                                             int num_rows, int max_q, int skip_small, int* error, cudaStream_t stream) {
+// chunk > 0: attention inside chunks of positions; softcap c > 0: scaled scores go through c * tanh(s / c) (see FaParams).
+extern "C" int pylon_paged_attention_tcgen05_masked(const void* q, long long q_stride, const void* k_pages, const void* v_pages, void* out,
+                                                    const int* q_start, const int* kv_len, const int* block_table, int table_width,
+                                                    int page_size, int num_pages, int nq, int nkv, int window, int chunk, float softcap,
+                                                    float scale, int first_row, int num_rows, int max_q, int skip_small, int* error,
+                                                    cudaStream_t stream) {
   if (num_rows <= 0) return 0;
+  if (chunk < 0 || softcap < 0.f) PYLON_REFUSE("paged_attention_tcgen05: chunk %d, soft cap %f", chunk, softcap);
   if (nkv < 1 || nq < 1 || nq % nkv) PYLON_REFUSE("paged_attention_tcgen05: %d query heads over %d KV heads", nq, nkv);
   if (page_size < 64 || page_size % 64) PYLON_REFUSE("paged_attention_tcgen05: pages of %d keys; a multiple of 64 is needed", page_size);
   if (table_width < 1 || window < 0 || max_q < 1) PYLON_REFUSE("paged_attention_tcgen05: table width %d, window %d, longest row %d", table_width, window, max_q);
@@ -551,10 +569,21 @@ extern "C" int pylon_paged_attention_tcgen05(const void* q, long long q_stride, 
   p.q_start = q_start; p.kv_len = kv_len; p.block_table = block_table;
   p.table_width = table_width; p.page_size = page_size; p.num_pages = num_pages;
   p.nq = nq; p.nkv = nkv; p.group = nq / nkv; p.window = window; p.skip_small = skip_small; p.first_row = first_row;
-  p.scale_log2 = scale * 1.4426950408889634f;
+  p.scale_log2 = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f;
+  p.chunk = chunk;
+  p.cap_pre = softcap > 0.f ? scale / softcap : 0.f;
   p.error = error;
   const long long q_tiles = ((long long)max_q * p.group + FA_BM - 1) / FA_BM;
   if (q_tiles > 65535) PYLON_REFUSE("paged_attention_tcgen05: too many query tiles");
   launch_dependent(attention_tcgen05_kernel, dim3(nkv, num_rows, (unsigned)q_tiles), dim3(FA_THREADS), FA_SMEM, stream, p, map_k, map_v);
   PYLON_CHECK_LAUNCH("paged_attention_tcgen05");
+}
+
+// The same without chunks and soft cap.
+extern "C" int pylon_paged_attention_tcgen05(const void* q, long long q_stride, const void* k_pages, const void* v_pages, void* out,
+                                             const int* q_start, const int* kv_len, const int* block_table, int table_width,
+                                             int page_size, int num_pages, int nq, int nkv, int window, float scale, int first_row,
+                                             int num_rows, int max_q, int skip_small, int* error, cudaStream_t stream) {
+  return pylon_paged_attention_tcgen05_masked(q, q_stride, k_pages, v_pages, out, q_start, kv_len, block_table, table_width, page_size,
+                                              num_pages, nq, nkv, window, 0, 0.f, scale, first_row, num_rows, max_q, skip_small, error, stream);
 }

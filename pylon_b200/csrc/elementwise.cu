@@ -640,11 +640,11 @@ __global__ void swiglu_bf16x8_kernel(const uint4* __restrict__ gate_up, uint4* _
 //   k head : normalised, written to its page slot [pages, nkv, page_size, d]
 //   v head : v <- (1 - lambda) v + lambda v_other[t] when v_other is given (lambda: a float32 on
 //            the device), written back in place and to its page slot [pages, nkv, page_size, dv]
-// v_other: rows of nkv * dv values with a row stride, in T; it may be another layer's qkv buffer.
+// v_other: rows of nkv heads, v_other_head values apart, with a row stride, in T; it may be another layer's qkv buffer.
 // -----------------------------------------------------------------------------------------
 template <typename T>
 __global__ void qk_norm_mix_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
-                                            float eps, const T* __restrict__ v_other, long long v_other_stride,
+                                            float eps, const T* __restrict__ v_other, long long v_other_stride, int v_other_head,
                                             const float* __restrict__ lambda, const int* __restrict__ positions,
                                             const int* __restrict__ token_row, const int* __restrict__ block_table, int table_width,
                                             int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int nq,
@@ -676,10 +676,10 @@ __global__ void qk_norm_mix_kv_write_kernel(T* __restrict__ qkv, const float* __
     const int kv_head = head - nq - nkv;
     T* src = row_base + (long long)(nq + nkv) * d + (long long)kv_head * dv;
     const float lam = v_other ? lambda[0] : 0.f;
-    const T* other = v_other ? v_other + (long long)t * v_other_stride + (long long)kv_head * dv : nullptr;
+    const T* other = v_other ? v_other + (long long)t * v_other_stride + (long long)kv_head * v_other_head : nullptr;
     for (int e = lane; e < dv; e += 32) {
       T value = src[e];
-      if (other) {
+      if (other && e < v_other_head) {   // the other layer may keep narrower heads: what lies beyond them here is padding
         value = from_float<T>((1.f - lam) * to_float<T>(value) + lam * to_float<T>(other[e]));
         src[e] = value;
       }
@@ -959,20 +959,20 @@ extern "C" int pylon_swiglu(const void* gate_up, void* out, int num_tokens, int 
 
 template <typename T>
 static int launch_qk_norm_mix(void* qkv, const float* qw, const float* kw, float eps, const void* v_other, long long v_other_stride,
-                              const float* lambda, const int* positions, const int* token_row, const int* block_table, int table_width,
+                              int v_other_head, const float* lambda, const int* positions, const int* token_row, const int* block_table, int table_width,
                               int page_size, void* k_pages, void* v_pages, int num_pages, int nq, int nkv, int d, int dv, int num_tokens,
                               int* error, cudaStream_t stream) {
   const int warps = 4;
   const long long items = (long long)num_tokens * (nq + 2 * nkv);
   qk_norm_mix_kv_write_kernel<T><<<(unsigned)((items + warps - 1) / warps), warps * 32, 0, stream>>>(
-      (T*)qkv, qw, kw, eps, (const T*)v_other, v_other_stride, lambda, positions, token_row, block_table, table_width, page_size,
+      (T*)qkv, qw, kw, eps, (const T*)v_other, v_other_stride, v_other_head, lambda, positions, token_row, block_table, table_width, page_size,
       (T*)k_pages, (T*)v_pages, num_pages, nq, nkv, d, dv, num_tokens, error);
   PYLON_CHECK_LAUNCH("qk_norm_mix_kv_write");
 }
 
 // See qk_norm_mix_kv_write_kernel.  A null weight leaves its heads as they are; a null v_other mixes nothing.
 extern "C" int pylon_qk_norm_mix_kv_write(void* qkv, const float* q_weight, const float* k_weight, float eps, const void* v_other,
-                                          long long v_other_stride, const float* lambda, const int* positions, const int* token_row,
+                                          long long v_other_stride, int v_other_head, const float* lambda, const int* positions, const int* token_row,
                                           const int* block_table, int table_width, int page_size, void* k_pages, void* v_pages,
                                           int num_pages, int nq, int nkv, int d, int dv, int num_tokens, int dtype, int* error,
                                           cudaStream_t stream) {
@@ -981,10 +981,10 @@ extern "C" int pylon_qk_norm_mix_kv_write(void* qkv, const float* q_weight, cons
     PYLON_REFUSE("qk_norm_mix_kv_write: sizes %d/%d, heads %d/%d, page size %d, table width %d", d, dv, nq, nkv, page_size, table_width);
   if ((v_other == nullptr) != (lambda == nullptr)) PYLON_REFUSE("qk_norm_mix_kv_write: other values and their weight go together");
   if (dtype == PYLON_DTYPE_F32)
-    return launch_qk_norm_mix<float>(qkv, q_weight, k_weight, eps, v_other, v_other_stride, lambda, positions, token_row, block_table,
+    return launch_qk_norm_mix<float>(qkv, q_weight, k_weight, eps, v_other, v_other_stride, v_other_head, lambda, positions, token_row, block_table,
                                      table_width, page_size, k_pages, v_pages, num_pages, nq, nkv, d, dv, num_tokens, error, stream);
   if (dtype == PYLON_DTYPE_BF16)
-    return launch_qk_norm_mix<__nv_bfloat16>(qkv, q_weight, k_weight, eps, v_other, v_other_stride, lambda, positions, token_row,
+    return launch_qk_norm_mix<__nv_bfloat16>(qkv, q_weight, k_weight, eps, v_other, v_other_stride, v_other_head, lambda, positions, token_row,
                                              block_table, table_width, page_size, k_pages, v_pages, num_pages, nq, nkv, d, dv, num_tokens,
                                              error, stream);
   PYLON_REFUSE("qk_norm_mix_kv_write: unknown dtype %d", dtype);

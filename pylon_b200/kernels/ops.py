@@ -178,7 +178,7 @@ _SIGNATURES = {
                                               c_int, c_void_p, c_void_p],
         "pylon_qk_norm": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "pylon_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
-        "pylon_qk_norm_mix_kv_write": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+        "pylon_qk_norm_mix_kv_write": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     },
     "streams.cu": {
@@ -218,12 +218,17 @@ _SIGNATURES = {
         "pylon_paged_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                                       c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+        "pylon_paged_attention_mma_masked": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int,
+                                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "pylon_attention_scratch_floats": [c_int, c_int, c_int, c_int, c_int, c_int],
         "pylon_attention_decode_blocks": [],
     },
     "attention_tcgen05.cu": {
         "pylon_paged_attention_tcgen05": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                           c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+        "pylon_paged_attention_tcgen05_masked": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                 c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     },
     "sampling.cu": {
         "pylon_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -812,7 +817,7 @@ def paged_attention(
     dv = v_pages.shape[3]
     _need(chunk is None or chunk >= 1, "paged_attention: a chunk holds at least one position")
     _need(softcap is None or softcap > 0, "paged_attention: a soft cap must be positive")
-    plain_scores = chunk is None and softcap is None and dv == d
+    same_width = dv == d   # the tensor-core kernels are built for values as wide as the keys
     tokens = q.shape[0]
     _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= nq * d and q.dtype == k_pages.dtype, "paged_attention: q must be [T, >= nq * d] in the cache dtype")
     _need(nq % nkv == 0, f"paged_attention: {nq} query heads over {nkv} KV heads")
@@ -827,7 +832,7 @@ def paged_attention(
     _need(out.shape == (tokens, nq * dv) and out.dtype == q.dtype and out.is_contiguous(), "paged_attention: out has the wrong shape or dtype")
     scale = 1.0 / math.sqrt(d) if scale is None else float(scale)
     _need(scale > 0, "paged_attention: the softmax scale must be positive")
-    if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and not force_simple and plain_scores:
+    if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and not force_simple and same_width:
         library = _library("attention_mma.cu", {"PYLON_HEAD_DIM": d})
         group = nq // nkv
         any_large = max_q * group > 16
@@ -848,9 +853,10 @@ def paged_attention(
                 large = [index for index, count in enumerate(row_tokens) if count * group > 16]
                 if large and large[-1] - large[0] + 1 == len(large):   # one run of rows: the scheduler puts decoded rows first
                     first_row, row_count = large[0], len(large)
-            _check(fast, fast.pylon_paged_attention_tcgen05(
+            _check(fast, fast.pylon_paged_attention_tcgen05_masked(
                 _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(q_start), _ptr(kv_len), _ptr(block_table),
-                block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), scale, first_row, row_count, int(max_q), int(maybe_small),
+                block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), int(chunk or 0), float(softcap or 0.0), scale,
+                first_row, row_count, int(max_q), int(maybe_small),
                 _ptr(attention_error_word(q.device)), _stream()))
             if not maybe_small:
                 return out
@@ -865,9 +871,10 @@ def paged_attention(
             scratch = torch.empty((floats,), dtype=torch.float32, device=q.device)
         if blocks:
             counters = _zeroed_counters(q.device, "attention", rows * nkv)
-        _check(library, library.pylon_paged_attention_mma(
+        _check(library, library.pylon_paged_attention_mma_masked(
             _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(scratch), _ptr(counters), _ptr(q_start), _ptr(kv_len),
-            _ptr(block_table), block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), scale, rows, tokens,
+            _ptr(block_table), block_table.shape[1], page_size, num_pages, nq, nkv, int(window or 0), int(chunk or 0), float(softcap or 0.0),
+            scale, rows, tokens,
             int(max_q), splits, blocks, int(use_tcgen05), int(bool(rows_alike)), _ptr(attention_error_word(q.device)), _stream()))
         return out
     _need(d <= 512 and dv <= 512, f"paged_attention: head sizes {d} / {dv}: at most 512")
@@ -896,12 +903,15 @@ def qk_norm_mix_kv_write(
     value_dim: int,
     other_values: Optional[torch.Tensor] = None,
     mix_weight: Optional[torch.Tensor] = None,
+    other_head_width: Optional[int] = None,
 ) -> torch.Tensor:
     """For attention without rotation, on ``qkv [T, nq * d + nkv * d + nkv * dv]``: RMSNorm each q and k head (when
     weights are given), q back in place, k into its page slot; every v head, mixed first with another layer's values
     of the same token when ``other_values [T, >= nkv * dv]`` (any row stride) and ``mix_weight`` (one float32 on the
     device, the share of the other values) are given - ``v = (1 - w) v + w other`` -, back in place and into its page
-    slot.  Returns ``qkv``: its first ``nq * d`` columns hold q, its last ``nkv * dv`` the values that were kept."""
+    slot.  ``other_head_width``: how far apart the heads of ``other_values`` lie (default ``dv``; another width when the
+    other layer keeps its values padded: only the columns that both have are mixed).  Returns ``qkv``: its first ``nq * d``
+    columns hold q, its last ``nkv * dv`` the values that were kept."""
     _need_cuda(qkv, q_weight, k_weight, positions, token_row, block_table, k_pages, v_pages, other_values, mix_weight)
     tokens = qkv.shape[0]
     _need(qkv.dim() == 2 and qkv.is_contiguous() and qkv.shape[1] == (nq + nkv) * head_dim + nkv * value_dim, "qk_norm_mix_kv_write: qkv must be contiguous [T, nq d + nkv d + nkv dv]")
@@ -916,14 +926,16 @@ def qk_norm_mix_kv_write(
               "qk_norm_mix_kv_write: pages must be contiguous [pages, nkv, page_size, width] in the activation dtype")
     _need((other_values is None) == (mix_weight is None), "qk_norm_mix_kv_write: other values and their weight go together")
     other_stride = 0
+    other_head_width = value_dim if other_head_width is None else int(other_head_width)
     if other_values is not None:
-        _need(other_values.dim() == 2 and other_values.shape == (tokens, nkv * value_dim) and other_values.stride(1) == 1 and other_values.dtype == qkv.dtype,
-              "qk_norm_mix_kv_write: other values must be [T, nkv * dv] in the activation dtype")
+        _need(other_head_width >= 1 and other_values.dim() == 2 and other_values.shape == (tokens, nkv * other_head_width)
+              and other_values.stride(1) == 1 and other_values.dtype == qkv.dtype,
+              "qk_norm_mix_kv_write: other values must be [T, nkv * other_head_width] in the activation dtype")
         _need(mix_weight.dtype == torch.float32 and mix_weight.numel() == 1, "qk_norm_mix_kv_write: the mixing weight is one float32")
         other_stride = other_values.stride(0)
     library = _library("elementwise.cu")
     _check(library, library.pylon_qk_norm_mix_kv_write(
-        _ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(other_values), other_stride, _ptr(mix_weight), _ptr(positions),
+        _ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(other_values), other_stride, other_head_width, _ptr(mix_weight), _ptr(positions),
         _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], nq, nkv,
         head_dim, value_dim, tokens, _dtype_code(qkv.dtype), _ptr(cache_write_error_word(k_pages.device)), _stream()))
     return qkv

@@ -72,6 +72,7 @@ class GroupedQueryAttention(Mixer):
             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "value_mix": "vmix", **(names or {}),
         }
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.mix_weight = None
+        self.kept_value_dim = self.value_dim   # the width values have in the cache: wider than value_dim when they are kept padded
 
     # -- weights -------------------------------------------------------------------------
     def tensors(self) -> Sequence[TensorDecl]:
@@ -90,9 +91,21 @@ class GroupedQueryAttention(Mixer):
 
     def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
         n = self.names
+        w_v, w_o = tensors[n["v"]], tensors[n["o"]]
+        # The tensor-core attention kernels take values as wide as the keys.  Narrower values are kept padded to the keys'
+        # width in bfloat16: zero rows in the value projection, zero columns in the output projection; the padding is zero
+        # from the product to the cache and meets zeros in the output product, so nothing else needs to know.
+        self.kept_value_dim = self.value_dim
+        if dtype == torch.bfloat16 and self.value_dim < self.head_dim and self.head_dim % 16 == 0 and self.head_dim <= 256:
+            self.kept_value_dim = self.head_dim
+            padded_v = w_v.new_zeros((self.n_kv_heads, self.head_dim, self.width))
+            padded_v[:, : self.value_dim] = w_v.view(self.n_kv_heads, self.value_dim, self.width)
+            padded_o = w_o.new_zeros((self.width, self.n_heads, self.head_dim))
+            padded_o[:, :, : self.value_dim] = w_o.view(self.width, self.n_heads, self.value_dim)
+            w_v, w_o = padded_v.view(-1, self.width), padded_o.view(self.width, -1)
         # q, k and v share one product: their matrices are stacked by rows at load.
-        self.w_qkv = torch.cat((tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]), dim=0).contiguous()
-        self.w_o = tensors[n["o"]].contiguous()
+        self.w_qkv = torch.cat((tensors[n["q"]], tensors[n["k"]], w_v), dim=0).contiguous()
+        self.w_o = w_o.contiguous()
         if self.qk_norm_eps is not None:
             self.q_norm, self.k_norm = tensors[n["q_norm"]].contiguous(), tensors[n["k_norm"]].contiguous()
         if self.value_mix == "mix":
@@ -103,7 +116,7 @@ class GroupedQueryAttention(Mixer):
 
     # -- cache ---------------------------------------------------------------------------
     def cache_need(self) -> CacheNeed:
-        value_dim = None if self.value_dim == self.head_dim else self.value_dim
+        value_dim = None if self.kept_value_dim == self.head_dim else self.kept_value_dim   # as kept: known once the weights are loaded
         return CacheNeed(kv=KVNeed(self.n_kv_heads, self.head_dim, self.window, value_dim, self.chunk))
 
     # -- run -----------------------------------------------------------------------------
@@ -148,16 +161,16 @@ class GroupedQueryAttention(Mixer):
         if self.position is not None:
             raise NotImplementedError("a position encoding together with value_dim, chunk, softcap or value_mix is not built")
         qkv = ops.linear(h, self.w_qkv)
-        other = step.carry.get(self.value_mix_key) if self.value_mix == "mix" else None
+        other, other_width = step.carry.get(self.value_mix_key, (None, None)) if self.value_mix == "mix" else (None, None)
         if self.value_mix == "mix" and other is None:
             raise RuntimeError(f"no earlier layer of this step left values under {self.value_mix_key!r}")
         ops.qk_norm_mix_kv_write(
             qkv, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, step.positions, step.token_row, cache.block_table, cache.page_size,
-            cache.k_pages, cache.v_pages, self.n_heads, self.n_kv_heads, self.head_dim, self.value_dim,
-            other_values=other, mix_weight=self.mix_weight if other is not None else None,
+            cache.k_pages, cache.v_pages, self.n_heads, self.n_kv_heads, self.head_dim, self.kept_value_dim,
+            other_values=other, mix_weight=self.mix_weight if other is not None else None, other_head_width=other_width,
         )
         if self.value_mix == "source":
-            step.carry[self.value_mix_key] = qkv[:, self.q_size + self.kv_size:]
+            step.carry[self.value_mix_key] = (qkv[:, self.q_size + self.kv_size:], self.kept_value_dim)
         context = ops.paged_attention(
             qkv, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
             self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale, row_tokens=step.row_tokens,

@@ -31,7 +31,7 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
 // proj: [T, ld] projections in T (columns [q | k | v | ...] from column 0; gate_a / gate_b name the columns of a and b).
-// conv_w: float32 [channels, taps] in the same channel order.  state: float32 [slots, slot_floats]; the convolution
+// conv_w: float32 [taps, channels] in the same channel order (tap by tap, so that a warp's channels lie side by side).  state: float32 [slots, slot_floats]; the convolution
 // inputs start at conv_offset.  qkv: float32 [T, channels] out.  gates: float32 [T, 2, heads] out (decay, beta).
 template <typename T, int MAX_TAPS>
 __global__ void delta_prepare_kernel(const T* __restrict__ proj, long long ld, const float* __restrict__ conv_w, int taps,
@@ -40,6 +40,8 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, long long ld, c
                                      float* __restrict__ qkv, float* __restrict__ gates, const float* __restrict__ a_log,
                                      const float* __restrict__ dt_bias, int col_a, int col_b, int heads, int kv_heads, int dim, int vdim,
                                      float unit_eps, int num_tokens) {
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int units = 2 * kv_heads + heads + 1;   // q heads, k heads, v heads, and one unit for the token's gates
@@ -63,23 +65,43 @@ __global__ void delta_prepare_kernel(const T* __restrict__ proj, long long ld, c
   const int first = is_value ? 2 * kv_heads * dim + (unit - 2 * kv_heads) * vdim : unit * dim;
   const int index = t - q_start[row];        // the token's place among the row's tokens of this step
   const float* old = state + (long long)slots[row] * slot_floats + conv_offset;   // [taps - 1, channels]
-  float sumsq = 0.f;
-  for (int e = lane; e < size; e += 32) {
-    const int c = first + e;
+  auto convolved = [&](int c) {
     float acc = 0.f;
-#pragma unroll
-    for (int j = 0; j < MAX_TAPS; ++j) {
-      if (j < taps) {
-        const int back = taps - 1 - j;       // how many tokens before this one
-        float input;
-        if (back <= index) input = to_float<T>(proj[(long long)(t - back) * ld + c]);
-        else input = old[(long long)(taps - 1 - (back - index)) * channels + c];
-        acc = fmaf(conv_w[(long long)c * taps + j], input, acc);
-      }
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;       // how many tokens before this one
+      float input;
+      if (back <= index) input = to_float<T>(proj[(long long)(t - back) * ld + c]);
+      else input = old[(long long)(taps - 1 - (back - index)) * channels + c];
+      acc = fmaf(conv_w[(long long)j * channels + c], input, acc);
     }
-    acc = silu_f(acc);
-    qkv[(long long)t * channels + c] = acc;   // values are done; queries and keys are scaled below
-    sumsq = fmaf(acc, acc, sumsq);
+    return silu_f(acc);
+  };
+  constexpr int KEPT = 8;   // heads of up to 256 channels stay in registers between the convolution and the scaling
+  float sumsq = 0.f;
+  if (size <= 32 * KEPT) {
+    float kept[KEPT];
+#pragma unroll
+    for (int n = 0; n < KEPT; ++n) {
+      const int e = lane + 32 * n;
+      kept[n] = e < size ? convolved(first + e) : 0.f;
+      sumsq = fmaf(kept[n], kept[n], sumsq);
+    }
+    float factor = 1.f;
+    if (!is_value) {
+      factor = rsqrtf(warp_sum(sumsq) + unit_eps);
+      if (unit < kv_heads) factor *= rsqrtf((float)dim);
+    }
+#pragma unroll
+    for (int n = 0; n < KEPT; ++n) {
+      const int e = lane + 32 * n;
+      if (e < size) qkv[(long long)t * channels + first + e] = is_value ? kept[n] : kept[n] * factor;
+    }
+    return;
+  }
+  for (int e = lane; e < size; e += 32) {
+    const float value = convolved(first + e);
+    qkv[(long long)t * channels + first + e] = value;   // values are done; queries and keys are scaled below
+    sumsq = fmaf(value, value, sumsq);
   }
   if (is_value) return;
   sumsq = warp_sum(sumsq);
@@ -94,6 +116,8 @@ template <typename T, int MAX_TAPS>
 __global__ void delta_conv_advance_kernel(const T* __restrict__ proj, long long ld, int taps, float* __restrict__ state,
                                           long long slot_floats, long long conv_offset, const int* __restrict__ q_start,
                                           const int* __restrict__ slots, int channels, int num_rows) {
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (item >= (long long)num_rows * channels) return;
   const int row = (int)(item / channels), c = (int)(item % channels);
@@ -113,21 +137,42 @@ __global__ void delta_conv_advance_kernel(const T* __restrict__ proj, long long 
     if (m < taps - 1) mine[(long long)m * channels + c] = kept[m];
 }
 
-// grid (slices of vdim, heads, rows); block = COLS columns x P lanes.  PER >= ceil(dim / P).
+__device__ __forceinline__ void delta_copy_async(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void delta_copy_async_16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void delta_copy_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void delta_copy_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// grid (slices of vdim, heads, rows); block = cols columns x P lanes (padded to a whole warp).  PER >= ceil(dim / P).
+// The walk over a row's tokens is a chain of dependent steps, so what a step waits for must be near: the tokens' keys,
+// queries, values, decay and beta come into shared memory `stage_tokens` tokens at a time by asynchronous copies, two
+// stages in turn, while the tokens of the stage before are walked.  Shared memory: 2 * stage_tokens * per_token floats, per_token
+// = 2 dim + cols + 2 rounded up to a multiple of 4.  `wide`: dim, vdim, cols and the buffers' addresses allow 16-byte copies (copies of
+// 4 bytes go through one by one: with them alone a token took 1,400 cycles).
 template <int PER>
 __global__ void delta_recurrence_kernel(const float* __restrict__ qkv, const float* __restrict__ gates, float* __restrict__ state,
                                         long long slot_floats, const int* __restrict__ q_start, const int* __restrict__ slots,
-                                        float* __restrict__ out, int heads, int kv_heads, int dim, int vdim, int lanes, int cols) {
+                                        float* __restrict__ out, int heads, int kv_heads, int dim, int vdim, int lanes, int cols,
+                                        int stage_tokens, int wide) {
+  extern __shared__ __align__(16) float stages[];
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const int P = lanes;
   const int p = threadIdx.x % P;
-  const int j = blockIdx.x * cols + threadIdx.x / P;   // my column of the head's matrix
+  const int column = threadIdx.x / P;                  // among the block's columns
+  const int j = blockIdx.x * cols + column;            // my column of the head's matrix
   const int head = blockIdx.y, row = blockIdx.z;
   const int begin = q_start[row], end = q_start[row + 1];
   if (end <= begin) return;
-  const bool live = j < vdim && (int)threadIdx.x / P < cols;   // a block is padded to a whole warp: the lanes beyond its columns only keep the shuffles whole
+  const bool live = j < vdim && column < cols;   // a block is padded to a whole warp: the lanes beyond its columns only keep the shuffles whole
   const int kv = head / (heads / kv_heads);
   const int channels = 2 * kv_heads * dim + heads * vdim;
-  const int q_col = kv * dim, k_col = kv_heads * dim + kv * dim, v_col = 2 * kv_heads * dim + head * vdim + j;
+  const int q_col = kv * dim, k_col = kv_heads * dim + kv * dim, v_col = 2 * kv_heads * dim + head * vdim + blockIdx.x * cols;
+  const int per_token = (2 * dim + cols + 2 + 3) & ~3;   // keys | queries | the block's values | decay | beta | padding
   float* mine = state + (long long)slots[row] * slot_floats + ((long long)head * dim) * vdim + j;   // S[i, j] at mine[i * vdim]
   float s[PER];
 #pragma unroll
@@ -135,43 +180,87 @@ __global__ void delta_recurrence_kernel(const float* __restrict__ qkv, const flo
     const int i = p + n * P;
     s[n] = (live && i < dim) ? mine[(long long)i * vdim] : 0.f;
   }
-  float k_next[PER], q_next[PER];
-  float g_next, beta_next, v_next;
-  auto fetch = [&](int t) {
-    const float* token = qkv + (long long)t * channels;
-#pragma unroll
-    for (int n = 0; n < PER; ++n) {
-      const int i = p + n * P;
-      k_next[n] = i < dim ? token[k_col + i] : 0.f;
-      q_next[n] = i < dim ? token[q_col + i] : 0.f;
+  auto fetch = [&](int first, int buffer) {
+    const int count = min(stage_tokens, end - first);
+    if (wide) {
+      const int units = (2 * dim + cols) >> 2;   // 16-byte units of a token: keys, queries, values
+      for (int x = threadIdx.x; x < count * units; x += blockDim.x) {
+        const int token = x / units, e = (x - token * units) << 2;
+        float* dst = stages + ((long long)buffer * stage_tokens + token) * per_token + e;
+        const float* src = qkv + (long long)(first + token) * channels;
+        if (e < dim) delta_copy_async_16(dst, src + k_col + e);
+        else if (e < 2 * dim) delta_copy_async_16(dst, src + q_col + (e - dim));
+        else if (blockIdx.x * cols + (e - 2 * dim) < vdim) delta_copy_async_16(dst, src + v_col + (e - 2 * dim));   // vdim is a multiple of 4: a unit is inside or outside
+        else dst[0] = dst[1] = dst[2] = dst[3] = 0.f;
+      }
+      for (int x = threadIdx.x; x < count * 2; x += blockDim.x) {
+        const int token = x >> 1;
+        delta_copy_async(stages + ((long long)buffer * stage_tokens + token) * per_token + 2 * dim + cols + (x & 1),
+                         gates + (long long)(first + token) * 2 * heads + ((x & 1) ? heads + head : head));
+      }
+      delta_copy_commit();
+      return;
     }
-    g_next = gates[(long long)t * 2 * heads + head];
-    beta_next = gates[(long long)t * 2 * heads + heads + head];
-    v_next = live ? token[v_col] : 0.f;
+    for (int token = 0; token < count; ++token) {
+      float* dst = stages + ((long long)buffer * stage_tokens + token) * per_token;
+      const float* src = qkv + (long long)(first + token) * channels;
+      const float* gate = gates + (long long)(first + token) * 2 * heads;
+      for (int e = threadIdx.x; e < 2 * dim + cols + 2; e += blockDim.x) {
+        if (e < dim) delta_copy_async(dst + e, src + k_col + e);
+        else if (e < 2 * dim) delta_copy_async(dst + e, src + q_col + (e - dim));
+        else if (e < 2 * dim + cols) {
+          const int c = e - 2 * dim;
+          if (blockIdx.x * cols + c < vdim) delta_copy_async(dst + e, src + v_col + c); else dst[e] = 0.f;
+        } else delta_copy_async(dst + e, gate + (e == 2 * dim + cols ? head : heads + head));
+      }
+    }
+    delta_copy_commit();
   };
-  fetch(begin);
-  for (int t = begin; t < end; ++t) {
-    float k[PER], q[PER];
-#pragma unroll
-    for (int n = 0; n < PER; ++n) { k[n] = k_next[n]; q[n] = q_next[n]; }
-    const float g = g_next, beta = beta_next, v = v_next;
-    if (t + 1 < end) fetch(t + 1);
-    float dot = 0.f;
-#pragma unroll
-    for (int n = 0; n < PER; ++n) {
-      s[n] *= g;
-      dot = fmaf(s[n], k[n], dot);
+  int buffer = 0;
+  fetch(begin, 0);
+  for (int first = begin; first < end; first += stage_tokens) {
+    if (first + stage_tokens < end) {
+      fetch(first + stage_tokens, buffer ^ 1);
+      delta_copy_wait<1>();
+    } else {
+      delta_copy_wait<0>();
     }
-    for (int offset = P >> 1; offset > 0; offset >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
-    const float w = beta * (v - dot);
-    float read = 0.f;
+    __syncthreads();
+    const int count = min(stage_tokens, end - first);
+    const float* staged = stages + (long long)buffer * stage_tokens * per_token;
+#pragma unroll 2
+    for (int token = 0; token < count; ++token) {
+      const float* here = staged + token * per_token;
+      float k[PER], q[PER];
 #pragma unroll
-    for (int n = 0; n < PER; ++n) {
-      s[n] = fmaf(k[n], w, s[n]);
-      read = fmaf(s[n], q[n], read);
+      for (int n = 0; n < PER; ++n) {
+        const int i = p + n * P;
+        k[n] = i < dim ? here[i] : 0.f;
+        q[n] = i < dim ? here[dim + i] : 0.f;
+      }
+      const float v = column < cols ? here[2 * dim + column] : 0.f;
+      const float g = here[2 * dim + cols], beta = here[2 * dim + cols + 1];
+      float dot[2] = {0.f, 0.f};   // two chains: the sums are chains of dependent steps
+#pragma unroll
+      for (int n = 0; n < PER; ++n) {
+        s[n] *= g;
+        dot[n & 1] = fmaf(s[n], k[n], dot[n & 1]);
+      }
+      float sum = dot[0] + dot[1];
+      for (int offset = P >> 1; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+      const float w = beta * (v - sum);
+      float read[2] = {0.f, 0.f};
+#pragma unroll
+      for (int n = 0; n < PER; ++n) {
+        s[n] = fmaf(k[n], w, s[n]);
+        read[n & 1] = fmaf(s[n], q[n], read[n & 1]);
+      }
+      float o = read[0] + read[1];
+      for (int offset = P >> 1; offset > 0; offset >>= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
+      if (live && p == 0) out[((long long)(first + token) * heads + head) * vdim + j] = o;
     }
-    for (int offset = P >> 1; offset > 0; offset >>= 1) read += __shfl_xor_sync(0xffffffffu, read, offset);
-    if (live && p == 0) out[((long long)t * heads + head) * vdim + j] = read;
+    __syncthreads();   // the stage is free to be filled again
+    buffer ^= 1;
   }
   if (live) {
 #pragma unroll
@@ -182,11 +271,121 @@ __global__ void delta_recurrence_kernel(const float* __restrict__ qkv, const flo
   }
 }
 
+// The same walk for the sizes models have, with everything that shapes the inner loop known to the compiler: dim = PER * P
+// exactly, P lanes to a column, PER a multiple of 4, 16-byte copies.  A lane holds entries (4 (m P + p) + c) of its column, c < 4,
+// m < PER / 4, so that the lanes of a column read a token's keys and queries as neighbouring 16-byte units (no bank conflicts, a
+// quarter of the loads), the shuffles unroll and no access needs a bound.  A token costs some 100 instructions this way; the
+// general kernel above, with its sizes at run time, took 680 (measured at dim 128: 0.48 us a token against 0.74 us with 4-byte copies).
+template <int PER, int P>
+__global__ void __launch_bounds__(128) delta_recurrence_exact_kernel(const float* __restrict__ qkv, const float* __restrict__ gates,
+                                                                     float* __restrict__ state, long long slot_floats,
+                                                                     const int* __restrict__ q_start, const int* __restrict__ slots,
+                                                                     float* __restrict__ out, int heads, int kv_heads, int vdim, int stage_tokens) {
+  constexpr int DIM = PER * P, COLS = 128 / P, PER_TOKEN = 2 * DIM + COLS + 4;   // keys | queries | the block's values | decay, beta, padding
+  extern __shared__ __align__(16) float stages[];
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
+  const int p = threadIdx.x % P, column = threadIdx.x / P;
+  const int j = blockIdx.x * COLS + column;
+  const int head = blockIdx.y, row = blockIdx.z;
+  const int begin = q_start[row], end = q_start[row + 1];
+  if (end <= begin) return;
+  const bool live = j < vdim;
+  const int kv = head / (heads / kv_heads);
+  const int channels = 2 * kv_heads * DIM + heads * vdim;
+  const int q_col = kv * DIM, k_col = kv_heads * DIM + kv * DIM, v_col = 2 * kv_heads * DIM + head * vdim + blockIdx.x * COLS;
+  float* mine = state + (long long)slots[row] * slot_floats + ((long long)head * DIM) * vdim + j;   // S[i, j] at mine[i * vdim]
+  float s[PER];
+#pragma unroll
+  for (int n = 0; n < PER; ++n) {
+    const int i = 4 * ((n >> 2) * P + p) + (n & 3);
+    s[n] = live ? mine[(long long)i * vdim] : 0.f;
+  }
+  auto fetch = [&](int first, int buffer) {
+    const int count = min(stage_tokens, end - first);
+    constexpr int UNITS = (2 * DIM + COLS) / 4;
+    for (int x = threadIdx.x; x < count * UNITS; x += 128) {
+      const int token = x / UNITS, e = (x - token * UNITS) << 2;
+      float* dst = stages + (buffer * stage_tokens + token) * PER_TOKEN + e;
+      const float* src = qkv + (long long)(first + token) * channels;
+      if (e < DIM) delta_copy_async_16(dst, src + k_col + e);
+      else if (e < 2 * DIM) delta_copy_async_16(dst, src + q_col + (e - DIM));
+      else if (blockIdx.x * COLS + (e - 2 * DIM) < vdim) delta_copy_async_16(dst, src + v_col + (e - 2 * DIM));
+      else dst[0] = dst[1] = dst[2] = dst[3] = 0.f;
+    }
+    for (int x = threadIdx.x; x < count * 2; x += 128) {
+      const int token = x >> 1;
+      delta_copy_async(stages + (buffer * stage_tokens + token) * PER_TOKEN + 2 * DIM + COLS + (x & 1),
+                       gates + (long long)(first + token) * 2 * heads + ((x & 1) ? heads + head : head));
+    }
+    delta_copy_commit();
+  };
+  int buffer = 0;
+  fetch(begin, 0);
+  for (int first = begin; first < end; first += stage_tokens) {
+    if (first + stage_tokens < end) {
+      fetch(first + stage_tokens, buffer ^ 1);
+      delta_copy_wait<1>();
+    } else {
+      delta_copy_wait<0>();
+    }
+    __syncthreads();
+    const int count = min(stage_tokens, end - first);
+    const float* staged = stages + buffer * stage_tokens * PER_TOKEN;
+    float* o_row = out + ((long long)first * heads + head) * vdim + j;
+#pragma unroll 2
+    for (int token = 0; token < count; ++token) {
+      const float* here = staged + token * PER_TOKEN;
+      float k[PER], q[PER];
+#pragma unroll
+      for (int m = 0; m < PER / 4; ++m) {
+        const float4 k4 = *reinterpret_cast<const float4*>(here + 4 * (m * P + p));
+        const float4 q4 = *reinterpret_cast<const float4*>(here + DIM + 4 * (m * P + p));
+        k[4 * m] = k4.x; k[4 * m + 1] = k4.y; k[4 * m + 2] = k4.z; k[4 * m + 3] = k4.w;
+        q[4 * m] = q4.x; q[4 * m + 1] = q4.y; q[4 * m + 2] = q4.z; q[4 * m + 3] = q4.w;
+      }
+      const float v = here[2 * DIM + column];
+      const float g = here[2 * DIM + COLS], beta = here[2 * DIM + COLS + 1];
+      float dot[2] = {0.f, 0.f};   // two chains: the sums are chains of dependent steps
+#pragma unroll
+      for (int n = 0; n < PER; ++n) {
+        s[n] *= g;
+        dot[n & 1] = fmaf(s[n], k[n], dot[n & 1]);
+      }
+      float sum = dot[0] + dot[1];
+#pragma unroll
+      for (int offset = P >> 1; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+      const float w = beta * (v - sum);
+      float read[2] = {0.f, 0.f};
+#pragma unroll
+      for (int n = 0; n < PER; ++n) {
+        s[n] = fmaf(k[n], w, s[n]);
+        read[n & 1] = fmaf(s[n], q[n], read[n & 1]);
+      }
+      float o = read[0] + read[1];
+#pragma unroll
+      for (int offset = P >> 1; offset > 0; offset >>= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
+      if (live && p == 0) o_row[(long long)token * heads * vdim] = o;
+    }
+    __syncthreads();   // the stage is free to be filled again
+    buffer ^= 1;
+  }
+  if (live) {
+#pragma unroll
+    for (int n = 0; n < PER; ++n) {
+      const int i = 4 * ((n >> 2) * P + p) + (n & 3);
+      mine[(long long)i * vdim] = s[n];
+    }
+  }
+}
+
 // o: float32 [T, heads, vdim]; gate: columns of proj from col_gate, [heads, vdim]; out [T, heads * vdim] in T.
 template <typename T>
 __global__ void delta_gated_norm_kernel(const float* __restrict__ o, const T* __restrict__ proj, long long ld, int col_gate,
                                         const float* __restrict__ weight, T* __restrict__ out, int heads, int vdim, float eps,
                                         int num_tokens) {
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * warps_per_block + warp;
@@ -206,7 +405,7 @@ __global__ void delta_gated_norm_kernel(const float* __restrict__ o, const T* __
 
 using namespace pylon;
 
-constexpr int DELTA_MAX_TAPS = 8;
+constexpr int DELTA_MAX_TAPS = 16;
 
 template <typename T>
 static int launch_delta(const void* proj_v, long long ld, const float* conv_w, int taps, float* state, long long slot_floats,
@@ -221,16 +420,33 @@ static int launch_delta(const void* proj_v, long long ld, const float* conv_w, i
   {
     const int warps = 4;
     const long long items = (long long)num_tokens * (2 * kv_heads + heads + 1);
-    delta_prepare_kernel<T, DELTA_MAX_TAPS><<<(unsigned)((items + warps - 1) / warps), warps * 32, 0, stream>>>(
+    launch_dependent(delta_prepare_kernel<T, DELTA_MAX_TAPS>, dim3((unsigned)((items + warps - 1) / warps)), dim3(warps * 32), 0, stream,
         proj, ld, conv_w, taps, state, slot_floats, conv_offset, token_row, q_start, slots, qkv, gates, a_log, dt_bias, col_a, col_b,
         heads, kv_heads, dim, vdim, unit_eps, num_tokens);
   }
   if (taps > 1) {
     const long long items = (long long)num_rows * channels;
-    delta_conv_advance_kernel<T, DELTA_MAX_TAPS><<<(unsigned)((items + 127) / 128), 128, 0, stream>>>(
+    launch_dependent(delta_conv_advance_kernel<T, DELTA_MAX_TAPS>, dim3((unsigned)((items + 127) / 128)), dim3(128), 0, stream,
         proj, ld, taps, state, slot_floats, conv_offset, q_start, slots, channels, num_rows);
   }
-  {
+  bool walked = false;
+  if (dim % 4 == 0 && vdim % 4 == 0 && (uintptr_t)qkv % 16 == 0) {
+    // the sizes models have: the kernel whose inner loop is fixed when it is compiled
+#define PYLON_DELTA_EXACT(PER_, P_)                                                                                                   \
+    if (!walked && dim == PER_ * P_) {                                                                                                 \
+      constexpr int COLS_ = 128 / P_, PER_TOKEN_ = 2 * PER_ * P_ + COLS_ + 4;                                                          \
+      int stage_tokens = 16;                                                                                                           \
+      while (stage_tokens > 1 && 2LL * stage_tokens * PER_TOKEN_ * (long long)sizeof(float) > 48 * 1024) stage_tokens /= 2;            \
+      launch_dependent(delta_recurrence_exact_kernel<PER_, P_>, dim3((vdim + COLS_ - 1) / COLS_, heads, num_rows), dim3(128),          \
+                       2ull * stage_tokens * PER_TOKEN_ * sizeof(float), stream, qkv, gates, state, slot_floats, q_start, slots, o,    \
+                       heads, kv_heads, vdim, stage_tokens);                                                                           \
+      walked = true;                                                                                                                   \
+    }
+    PYLON_DELTA_EXACT(4, 8) PYLON_DELTA_EXACT(8, 8) PYLON_DELTA_EXACT(12, 8) PYLON_DELTA_EXACT(16, 8) PYLON_DELTA_EXACT(12, 16)
+    PYLON_DELTA_EXACT(16, 16) PYLON_DELTA_EXACT(12, 32) PYLON_DELTA_EXACT(16, 32)
+#undef PYLON_DELTA_EXACT
+  }
+  if (!walked) {
     // P lanes share a column: the fewest (a power of two, at least 4) that leave a lane at most 16 entries, so a block of
     // 128 threads owns 32 columns at most and the slices of vdim fill the device also with few heads.
     int lanes = 4;
@@ -240,8 +456,14 @@ static int launch_delta(const void* proj_v, long long ld, const float* conv_w, i
     while (cols > 1 && cols / 2 >= vdim) cols /= 2;
     dim3 grid((vdim + cols - 1) / cols, heads, num_rows);
     const int threads = cols * lanes;   // a multiple of 32 unless one warp holds all columns; shuffles stay inside groups of P lanes
+    // tokens per stage: 16, or as many as two stages of leave under 48 KB (at least 2 for every dim this entry takes)
+    const int per_token = (2 * dim + cols + 2 + 3) & ~3;
+    const int wide = dim % 4 == 0 && vdim % 4 == 0 && cols % 4 == 0 && (uintptr_t)qkv % 16 == 0;
+    int stage_tokens = 16;
+    while (stage_tokens > 1 && 2LL * stage_tokens * per_token * (long long)sizeof(float) > 48 * 1024) stage_tokens /= 2;
+    const size_t smem = 2ull * stage_tokens * per_token * sizeof(float);
 #define PYLON_DELTA_RECURRENCE(N) \
-    delta_recurrence_kernel<N><<<grid, threads < 32 ? 32 : threads, 0, stream>>>(qkv, gates, state, slot_floats, q_start, slots, o, heads, kv_heads, dim, vdim, lanes, cols)
+    launch_dependent(delta_recurrence_kernel<N>, grid, dim3(threads < 32 ? 32 : threads), smem, stream, qkv, gates, state, slot_floats, q_start, slots, o, heads, kv_heads, dim, vdim, lanes, cols, stage_tokens, wide)
     if (per <= 4) PYLON_DELTA_RECURRENCE(4);
     else if (per <= 8) PYLON_DELTA_RECURRENCE(8);
     else if (per <= 16) PYLON_DELTA_RECURRENCE(16);
@@ -251,7 +473,7 @@ static int launch_delta(const void* proj_v, long long ld, const float* conv_w, i
   {
     const int warps = 4;
     const long long items = (long long)num_tokens * heads;
-    delta_gated_norm_kernel<T><<<(unsigned)((items + warps - 1) / warps), warps * 32, 0, stream>>>(
+    launch_dependent(delta_gated_norm_kernel<T>, dim3((unsigned)((items + warps - 1) / warps)), dim3(warps * 32), 0, stream,
         o, proj, ld, col_gate, norm_weight, out, heads, vdim, norm_eps, num_tokens);
   }
   PYLON_CHECK_LAUNCH("gated_delta_rule");

@@ -649,6 +649,8 @@ __global__ void qk_norm_mix_kv_write_kernel(T* __restrict__ qkv, const float* __
                                             const int* __restrict__ token_row, const int* __restrict__ block_table, int table_width,
                                             int page_size, T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int nq,
                                             int nkv, int d, int dv, int num_tokens, int* __restrict__ error) {
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = nq + 2 * nkv;
@@ -964,7 +966,7 @@ static int launch_qk_norm_mix(void* qkv, const float* qw, const float* kw, float
                               int* error, cudaStream_t stream) {
   const int warps = 4;
   const long long items = (long long)num_tokens * (nq + 2 * nkv);
-  qk_norm_mix_kv_write_kernel<T><<<(unsigned)((items + warps - 1) / warps), warps * 32, 0, stream>>>(
+  launch_dependent(qk_norm_mix_kv_write_kernel<T>, dim3((unsigned)((items + warps - 1) / warps)), dim3(warps * 32), 0, stream,
       (T*)qkv, qw, kw, eps, (const T*)v_other, v_other_stride, v_other_head, lambda, positions, token_row, block_table, table_width, page_size,
       (T*)k_pages, (T*)v_pages, num_pages, nq, nkv, d, dv, num_tokens, error);
   PYLON_CHECK_LAUNCH("qk_norm_mix_kv_write");

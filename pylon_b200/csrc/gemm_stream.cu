@@ -74,7 +74,8 @@ __device__ __forceinline__ void st_mma(float (&c)[4], const unsigned (&a)[4], un
 // bfloat16 [M, N / 2] (ST_SWIGLU), row stride ldy for the last two.  error: 1 the producer, 2 a consumer gave up waiting.
 template <int MT, int FORM>
 __global__ void __launch_bounds__(ST_THREADS, 3) gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                                                                     void* __restrict__ y, int M, int N, int K, long long ldy, int* __restrict__ error) {
+                                                                     void* __restrict__ y, int M, int N, int K, long long ldy, int* __restrict__ error,
+                                                                     float unit_limit, float unit_alpha) {
   using Ring = StreamRing<MT>;
   constexpr int STAGES = Ring::STAGES, STAGE_BYTES = Ring::STAGE_BYTES;
   extern __shared__ unsigned char smem_raw[];
@@ -182,8 +183,13 @@ __global__ void __launch_bounds__(ST_THREADS, 3) gemm_stream_kernel(const __grid
         if (row0 + 8 < N) out[row0 + 8] = __float2bfloat16_rn(v[2 + e]);
       } else {   // rows row0 (gate) and row0 + 8 (its up row) are both this lane's
         if (row0 + 8 < N) {
-          const float gate = v[e], up = v[2 + e];
-          reinterpret_cast<__nv_bfloat16*>(y)[(size_t)m * ldy + (n0 + (warp - 1) * 16) / 2 + g] = __float2bfloat16_rn(__fdividef(gate, 1.f + __expf(-gate)) * up);   // approximate division: ample for bfloat16, no slow path
+          float gate = v[e], up = v[2 + e], gain = 1.f;
+          if (unit_limit > 0.f) {   // the clamped unit: min(gate, limit) * sigmoid(alpha * gate) * (clamp(up, -limit, limit) + 1)
+            gate = fminf(gate, unit_limit);
+            up = fminf(fmaxf(up, -unit_limit), unit_limit) + 1.f;
+            gain = unit_alpha;
+          }
+          reinterpret_cast<__nv_bfloat16*>(y)[(size_t)m * ldy + (n0 + (warp - 1) * 16) / 2 + g] = __float2bfloat16_rn(__fdividef(gate, 1.f + __expf(-gain * gate)) * up);   // approximate division: ample for bfloat16, no slow path
         }
       }
     }
@@ -240,7 +246,7 @@ static bool matrix_map(CUtensorMap* map, const void* base, long long rows, long 
 
 template <int MT, int FORM>
 static int launch_stream(const CUtensorMap& map_w, const CUtensorMap& map_x, void* y, int M, int N, int K, long long ldy, int parts, int slabs,
-                         int* error, cudaStream_t stream) {
+                         int* error, cudaStream_t stream, float unit_limit, float unit_alpha) {
   auto kernel = gemm_stream_kernel<MT, FORM>;
   static bool configured_on[pylon::MAX_DEVICES] = {};   // function attributes belong to a device
   bool& configured = configured_on[pylon::current_device_slot()];
@@ -249,13 +255,13 @@ static int launch_stream(const CUtensorMap& map_w, const CUtensorMap& map_x, voi
     if (err != cudaSuccess) PYLON_REFUSE("gemm_stream: %s", cudaGetErrorString(err));
     configured = true;
   }
-  launch_dependent<LAUNCH_GEMM>(kernel, dim3(parts, slabs), dim3(ST_THREADS), StreamRing<MT>::SMEM, stream, map_w, map_x, y, M, N, K, ldy, error);
+  launch_dependent<LAUNCH_GEMM>(kernel, dim3(parts, slabs), dim3(ST_THREADS), StreamRing<MT>::SMEM, stream, map_w, map_x, y, M, N, K, ldy, error, unit_limit, unit_alpha);
   PYLON_CHECK_LAUNCH("gemm_stream");
 }
 
 template <int FORM>
 static int dispatch_stream(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw, long long ldy, int parts,
-                           int* error, cudaStream_t stream, const char* name) {
+                           int* error, cudaStream_t stream, const char* name, float unit_limit = 0.f, float unit_alpha = 1.f) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64) PYLON_REFUSE("%s: M = %d is more than 64 rows", name, M);
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) PYLON_REFUSE("%s: K = %d and the row strides must be multiples of 8", name, K);
@@ -267,10 +273,10 @@ static int dispatch_stream(const void* x, const void* w, void* y, int M, int N, 
   const int tiles = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
   CUtensorMap map_w, map_x;
   if (!matrix_map(&map_w, w, N, K, ldw, ST_ROWS) || !matrix_map(&map_x, x, M, K, ldx, 8 * tiles)) PYLON_REFUSE("%s: the tensor maps could not be made", name);
-  if (tiles == 1) return launch_stream<1, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream);
-  if (tiles == 2) return launch_stream<2, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream);
-  if (tiles == 4) return launch_stream<4, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream);
-  return launch_stream<8, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream);
+  if (tiles == 1) return launch_stream<1, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream, unit_limit, unit_alpha);
+  if (tiles == 2) return launch_stream<2, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream, unit_limit, unit_alpha);
+  if (tiles == 4) return launch_stream<4, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream, unit_limit, unit_alpha);
+  return launch_stream<8, FORM>(map_w, map_x, y, M, N, K, ldy, parts, slabs, error, stream, unit_limit, unit_alpha);
 }
 
 }  // namespace pylon
@@ -297,4 +303,12 @@ extern "C" int pylon_gemm_stream_swiglu(const void* x, const void* w, void* y, i
                                         long long ldy, int* error, cudaStream_t stream) {
   if (N % 16 || ldy < N / 2) PYLON_REFUSE("gemm_stream_swiglu: N = %d must be a multiple of 16 and the result N / 2 columns wide", N);
   return pylon::dispatch_stream<pylon::ST_SWIGLU>(x, w, y, M, N, K, ldx, ldw, ldy, 1, error, stream, "gemm_stream_swiglu");
+}
+
+// The same with the clamped gated unit: g = min(x gate^T, limit), u = clamp(x up^T, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1).
+extern "C" int pylon_gemm_stream_glu_clamped(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,
+                                             long long ldy, float limit, float alpha, int* error, cudaStream_t stream) {
+  if (N % 16 || ldy < N / 2) PYLON_REFUSE("gemm_stream_glu_clamped: N = %d must be a multiple of 16 and the result N / 2 columns wide", N);
+  if (!(limit > 0.f)) PYLON_REFUSE("gemm_stream_glu_clamped: the limit must be positive");
+  return pylon::dispatch_stream<pylon::ST_SWIGLU>(x, w, y, M, N, K, ldx, ldw, ldy, 1, error, stream, "gemm_stream_glu_clamped", limit, alpha);
 }

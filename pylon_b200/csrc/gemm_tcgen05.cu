@@ -116,6 +116,13 @@ __host__ __device__ constexpr uint32_t tc_instr_desc(int m, int n) {
 // silu for a bfloat16 result.  The approximate division has no slow path: the exact one takes a subroutine for a zero
 // numerator, and the rows of a last, partly filled tile are all zeros (a 1,984-row product took 167 us instead of 146).
 __device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+__device__ __forceinline__ float gated_unit_fast(float g, float u, float limit, float alpha) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    return __fdividef(g, 1.f + __expf(-alpha * g)) * (fminf(fmaxf(u, -limit), limit) + 1.f);
+  }
+  return silu_fast(g) * u;
+}
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -166,6 +173,9 @@ struct RotateArgs {
   __nv_bfloat16* v_pages;
   int num_pages, nq, nkv;
   int* page_error;                 // set to PYLON_ERROR_BAD_PAGE when a block table names a page that is not there
+  // the gated unit of a SWIGLU epilogue: limit 0 is silu(gate) * up; limit > 0 the clamped unit,
+  // min(gate, limit) * sigmoid(alpha * min(gate, limit)) * (clamp(up, -limit, limit) + 1)
+  float unit_limit = 0.f, unit_alpha = 1.f;
 };
 enum TcMode { TC_PLAIN = 0, TC_SWIGLU = 1, TC_ROTATE = 2 };
 
@@ -412,7 +422,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
               for (int j = 0; j < 8; j += 2) {
                 const float g0 = __uint_as_float(raw[group * 16 + j]), g1 = __uint_as_float(raw[group * 16 + j + 1]);
                 const float u0 = __uint_as_float(raw[group * 16 + 8 + j]), u1 = __uint_as_float(raw[group * 16 + 8 + j + 1]);
-                packed[group * 4 + j / 2] = pack2(silu_fast(g0) * u0, silu_fast(g1) * u1);
+                packed[group * 4 + j / 2] = pack2(gated_unit_fast(g0, u0, rot.unit_limit, rot.unit_alpha), gated_unit_fast(g1, u1, rot.unit_limit, rot.unit_alpha));
               }
           } else {
 #pragma unroll
@@ -488,7 +498,7 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
 
 template <int BN, bool SWIGLU>
 static int launch_tcgen05(const CUtensorMap& map_a, const CUtensorMap& map_b, __nv_bfloat16* c, int M, int N, int K, long long ldc,
-                          int* error, int sm_count, cudaStream_t stream) {
+                          int* error, int sm_count, cudaStream_t stream, float unit_limit = 0.f, float unit_alpha = 1.f) {
   auto kernel = gemm_tcgen05_kernel<BN, SWIGLU ? TC_SWIGLU : TC_PLAIN, 128>;
   static bool configured_on[pylon::MAX_DEVICES] = {};   // function attributes belong to a device
   bool& configured = configured_on[pylon::current_device_slot()];
@@ -501,7 +511,10 @@ static int launch_tcgen05(const CUtensorMap& map_a, const CUtensorMap& map_b, __
   if (!make_map(&map_c, c, M, SWIGLU ? N / 2 : N, ldc, 32, TcStore<BN, SWIGLU>::COLUMNS)) PYLON_REFUSE("gemm_tcgen05: the output's tensor map could not be made");
   const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
   const int blocks = tiles < sm_count ? tiles : sm_count;
-  launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks), dim3(TC_THREADS), TcShared<BN>::BYTES, stream, map_a, map_b, map_c, M, N, K, error, RotateArgs{});
+  RotateArgs unit{};
+  unit.unit_limit = unit_limit;
+  unit.unit_alpha = unit_alpha;
+  launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks), dim3(TC_THREADS), TcShared<BN>::BYTES, stream, map_a, map_b, map_c, M, N, K, error, unit);
   PYLON_CHECK_LAUNCH("gemm_tcgen05");
 }
 
@@ -537,8 +550,8 @@ extern "C" int pylon_gemm_tcgen05_force_tile(int columns) {
 // (row stride ldy).  K and the strides multiples of 8, N a multiple of 8 (16 with swiglu), x, w and y 16-byte aligned.
 // swiglu != 0: w's rows alternate in groups of 8 between gate and up rows and y receives silu(gate) * up.
 // error: one int in device memory; the kernel sets it non-zero if one of its waits ran out (the result is then void).
-extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,
-                                       long long ldy, int swiglu, int* error, int sm_count, cudaStream_t stream) {
+static int gemm_tcgen05_entry(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,
+                             long long ldy, int swiglu, float unit_limit, float unit_alpha, int* error, int sm_count, cudaStream_t stream) {
   using namespace pylon;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldy % 8) PYLON_REFUSE("gemm_tcgen05: K = %d and the row strides must be multiples of 8", K);
@@ -568,15 +581,28 @@ extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, in
   __nv_bfloat16* out = (__nv_bfloat16*)y;
 #define PYLON_TC_CASE(BN_)                                                                                          \
   if (bn == BN_) {                                                                                                  \
-    if (swiglu) return launch_tcgen05<BN_, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);         \
+    if (swiglu) return launch_tcgen05<BN_, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream, unit_limit, unit_alpha); \
     return launch_tcgen05<BN_, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);                    \
   }
   PYLON_TC_CASE(256) PYLON_TC_CASE(192)
 #undef PYLON_TC_CASE
   if (bn == 288) return launch_tcgen05<288, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
   if (bn == 160) return launch_tcgen05<160, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
-  if (swiglu) return launch_tcgen05<128, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
+  if (swiglu) return launch_tcgen05<128, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream, unit_limit, unit_alpha);
   return launch_tcgen05<128, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
+}
+
+extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,
+                                       long long ldy, int swiglu, int* error, int sm_count, cudaStream_t stream) {
+  return gemm_tcgen05_entry(x, w, y, M, N, K, ldx, ldw, ldy, swiglu, 0.f, 1.f, error, sm_count, stream);
+}
+
+// The product of interleaved gate and up rows with the clamped gated unit in its epilogue: g = min(gate, limit),
+// u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + 1); y bfloat16 [M, N / 2].
+extern "C" int pylon_gemm_tcgen05_glu_clamped(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,
+                                              long long ldy, float limit, float alpha, int* error, int sm_count, cudaStream_t stream) {
+  if (!(limit > 0.f)) PYLON_REFUSE("gemm_tcgen05_glu_clamped: the limit must be positive");
+  return gemm_tcgen05_entry(x, w, y, M, N, K, ldx, ldw, ldy, 1, limit, alpha, error, sm_count, stream);
 }
 
 // The fused QKV product with its heads finished in the epilogue: x bfloat16 [M, K], w bfloat16 [(nq + 2 nkv) * d, K] (q rows,

@@ -24,21 +24,40 @@ namespace pylon {
 
 constexpr int MAX_STREAMS = 8;
 
-template <typename TD, typename TO>
+template <typename TD, int V>
+__device__ __forceinline__ void load_delta(const TD* src, float (&dst)[V]) {
+  if constexpr (V == 4 && sizeof(TD) == 2) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(src);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    dst[0] = a.x; dst[1] = a.y; dst[2] = b.x; dst[3] = b.y;
+  } else if constexpr (V == 4) {
+    const float4 raw = *reinterpret_cast<const float4*>(src);
+    dst[0] = raw.x; dst[1] = raw.y; dst[2] = raw.z; dst[3] = raw.w;
+  } else {
+    dst[0] = to_float<TD>(src[0]);
+  }
+}
+
+// V: columns a thread handles at once (4: 16-byte accesses, for widths that are multiples of 4 and aligned rows; else 1).
+template <typename TD, typename TO, int V>
 __global__ void streams_update_norm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int delta_parts, long long part_stride,
                                            float scale, const float* __restrict__ mix, const float* __restrict__ outw,
                                            const float* __restrict__ read, const float* __restrict__ weight, const int* __restrict__ rows,
                                            TO* __restrict__ out, int streams, int width, float eps, int kind) {
-  extern __shared__ float shared[];
+  extern __shared__ __align__(16) float shared[];
   float* u_row = shared;                 // [width]
   float* scratch = u_row + width;        // [34]
   float* coef = scratch + 34;            // mix [S * S], out [S], read [S]
   const int S = streams;
+  // the routes are weights of the model: they are read while the kernel ahead is still running
   for (int i = threadIdx.x; i < S * S; i += blockDim.x) coef[i] = mix ? mix[i] : (i / S == i % S ? 1.f : 0.f);
   for (int i = threadIdx.x; i < S; i += blockDim.x) {
     coef[S * S + i] = (outw ? outw[i] : 1.f) * scale;
     coef[S * S + S + i] = read ? read[i] : 1.f;
   }
+  grid_dependency_wait();
+  allow_dependents();   // only now: a kernel that is itself still waiting must not pull the next one onto the SMs
   __syncthreads();
   const float* c_mix = coef;
   const float* c_out = coef + S * S;
@@ -48,44 +67,97 @@ __global__ void streams_update_norm_kernel(float* __restrict__ x, const TD* __re
   float* xt = x + t * (long long)S * width;
   const bool update = delta != nullptr || mix != nullptr;
   float local_sum = 0.f;
-  for (int e = threadIdx.x; e < width; e += blockDim.x) {
-    float old[MAX_STREAMS];
+  for (int e = threadIdx.x * V; e < width; e += blockDim.x * V) {
+    float old[MAX_STREAMS][V];
 #pragma unroll
-    for (int s = 0; s < MAX_STREAMS; ++s) old[s] = s < S ? xt[(long long)s * width + e] : 0.f;
-    float y = 0.f;
-    if (delta) {
-      for (int part = 0; part < delta_parts; ++part) y += to_float<TD>(delta[part * part_stride + t * width + e]);
+    for (int s = 0; s < MAX_STREAMS; ++s) {
+      if (s < S) {
+        if constexpr (V == 4) {
+          const float4 raw = *reinterpret_cast<const float4*>(xt + (long long)s * width + e);
+          old[s][0] = raw.x; old[s][1] = raw.y; old[s][2] = raw.z; old[s][3] = raw.w;
+        } else {
+          old[s][0] = xt[(long long)s * width + e];
+        }
+      } else {
+#pragma unroll
+        for (int v = 0; v < V; ++v) old[s][v] = 0.f;
+      }
     }
-    float u = 0.f;
+    float y[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) y[v] = 0.f;
+    if (delta) {
+      for (int part = 0; part < delta_parts; ++part) {
+        float piece[V];
+        load_delta<TD, V>(delta + part * part_stride + t * width + e, piece);
+#pragma unroll
+        for (int v = 0; v < V; ++v) y[v] += piece[v];
+      }
+    }
+    float u[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) u[v] = 0.f;
 #pragma unroll
     for (int to = 0; to < MAX_STREAMS; ++to) {
       if (to < S) {
-        float value = old[to];
+        float value[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) value[v] = old[to][v];
         if (update) {
-          value = 0.f;
+#pragma unroll
+          for (int v = 0; v < V; ++v) value[v] = 0.f;
 #pragma unroll
           for (int from = 0; from < MAX_STREAMS; ++from)
-            if (from < S) value = fmaf(c_mix[from * S + to], old[from], value);
-          value = fmaf(c_out[to], y, value);
-          if (!rows) xt[(long long)to * width + e] = value;
+            if (from < S) {
+#pragma unroll
+              for (int v = 0; v < V; ++v) value[v] = fmaf(c_mix[from * S + to], old[from][v], value[v]);
+            }
+#pragma unroll
+          for (int v = 0; v < V; ++v) value[v] = fmaf(c_out[to], y[v], value[v]);
+          if (!rows) {
+            if constexpr (V == 4) *reinterpret_cast<float4*>(xt + (long long)to * width + e) = make_float4(value[0], value[1], value[2], value[3]);
+            else xt[(long long)to * width + e] = value[0];
+          }
         }
-        u = fmaf(c_read[to], value, u);
+#pragma unroll
+        for (int v = 0; v < V; ++v) u[v] = fmaf(c_read[to], value[v], u[v]);
       }
     }
-    u_row[e] = u;
-    local_sum += u;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      u_row[e + v] = u[v];
+      local_sum += u[v];
+    }
   }
   if (!out) return;
   float mean = 0.f;
   if (kind == 0) mean = block_sum(local_sum, scratch) / (float)width;
   float local_sq = 0.f;
-  for (int e = threadIdx.x; e < width; e += blockDim.x) {   // each thread reads back what it wrote itself
-    const float c = u_row[e] - mean;
-    local_sq = fmaf(c, c, local_sq);
+  for (int e = threadIdx.x * V; e < width; e += blockDim.x * V) {   // each thread reads back what it wrote itself
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      const float c = u_row[e + v] - mean;
+      local_sq = fmaf(c, c, local_sq);
+    }
   }
   const float inv = rsqrtf(block_sum(local_sq, scratch) / (float)width + eps);
   TO* orow = out + (long long)n * width;
-  for (int e = threadIdx.x; e < width; e += blockDim.x) orow[e] = from_float<TO>((u_row[e] - mean) * inv * weight[e]);
+  for (int e = threadIdx.x * V; e < width; e += blockDim.x * V) {
+    float result[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) result[v] = (u_row[e + v] - mean) * inv * weight[e + v];
+    if constexpr (V == 4 && sizeof(TO) == 2) {
+      const __nv_bfloat162 a = __floats2bfloat162_rn(result[0], result[1]), b = __floats2bfloat162_rn(result[2], result[3]);
+      uint2 packed;
+      packed.x = *reinterpret_cast<const unsigned*>(&a);
+      packed.y = *reinterpret_cast<const unsigned*>(&b);
+      *reinterpret_cast<uint2*>(orow + e) = packed;
+    } else if constexpr (V == 4) {
+      *reinterpret_cast<float4*>(orow + e) = make_float4(result[0], result[1], result[2], result[3]);
+    } else {
+      orow[e] = from_float<TO>(result[0]);
+    }
+  }
 }
 
 }  // namespace pylon
@@ -108,18 +180,23 @@ extern "C" int pylon_streams_update_norm(float* x, const void* delta, int delta_
   if (!out && rows) PYLON_REFUSE("streams_update_norm: a row selection without an output does nothing");
   if (delta && delta_parts < 1) PYLON_REFUSE("streams_update_norm: %d parts", delta_parts);
   if (delta && delta_parts > 1 && delta_dtype != PYLON_DTYPE_F32) PYLON_REFUSE("streams_update_norm: partial sums are float32");
-  const int threads = width >= 4096 ? 512 : (width >= 1024 ? 256 : 128);
+  const int threads = width >= 8192 ? 512 : (width >= 1024 ? 256 : 128);
   const size_t smem = (size_t)(width + 34 + streams * streams + 2 * streams) * sizeof(float);
   const long long part_stride = (long long)tokens * width;
-#define PYLON_STREAMS_LAUNCH(TD, TO)                                                                                          \
-  do {                                                                                                                        \
-    static bool raised[MAX_DEVICES] = {};                                                                                     \
-    if (smem > 48 * 1024 && !raised[current_device_slot()]) {                                                                 \
-      cudaFuncSetAttribute(streams_update_norm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);      \
-      raised[current_device_slot()] = true;                                                                                   \
-    }                                                                                                                         \
-    streams_update_norm_kernel<TD, TO><<<n_rows, threads, smem, stream>>>(x, (const TD*)delta, delta_parts, part_stride,      \
-        scale, mix, outw, read, weight, rows, (TO*)out, streams, width, eps, kind);                                           \
+  const bool vector = width % 4 == 0 && ((uintptr_t)x % 16 == 0) && (!delta || (uintptr_t)delta % 16 == 0) && (!out || (uintptr_t)out % 16 == 0);
+#define PYLON_STREAMS_LAUNCH_V(TD, TO, V)                                                                                        \
+  do {                                                                                                                           \
+    static bool raised[MAX_DEVICES] = {};                                                                                        \
+    if (smem > 48 * 1024 && !raised[current_device_slot()]) {                                                                    \
+      cudaFuncSetAttribute(streams_update_norm_kernel<TD, TO, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);      \
+      raised[current_device_slot()] = true;                                                                                      \
+    }                                                                                                                            \
+    launch_dependent(streams_update_norm_kernel<TD, TO, V>, dim3(n_rows), dim3(threads), smem, stream, x, (const TD*)delta,      \
+                     delta_parts, part_stride, scale, mix, outw, read, weight, rows, (TO*)out, streams, width, eps, kind);       \
+  } while (0)
+#define PYLON_STREAMS_LAUNCH(TD, TO)                                                      \
+  do {                                                                                    \
+    if (vector) PYLON_STREAMS_LAUNCH_V(TD, TO, 4); else PYLON_STREAMS_LAUNCH_V(TD, TO, 1); \
   } while (0)
   const bool delta_f32 = !delta || delta_dtype == PYLON_DTYPE_F32;
   if (!delta_f32 && delta_dtype != PYLON_DTYPE_BF16) PYLON_REFUSE("streams_update_norm: unknown delta dtype %d", delta_dtype);
@@ -131,5 +208,6 @@ extern "C" int pylon_streams_update_norm(float* x, const void* delta, int delta_
     PYLON_REFUSE("streams_update_norm: unknown output dtype %d", out_dtype);
   }
 #undef PYLON_STREAMS_LAUNCH
+#undef PYLON_STREAMS_LAUNCH_V
   PYLON_CHECK_LAUNCH("streams_update_norm");
 }

@@ -200,10 +200,13 @@ _SIGNATURES = {
         "pylon_gemm_stream_partial": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p],
         "pylon_gemm_stream_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p],
         "pylon_gemm_stream_swiglu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p],
+        "pylon_gemm_stream_glu_clamped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_float, c_float, c_void_p, c_void_p],
     },
     "gemm_tcgen05.cu": {
         "pylon_gemm_tcgen05_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
                                     c_void_p, c_int, c_void_p],
+        "pylon_gemm_tcgen05_glu_clamped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_float, c_float,
+                                           c_void_p, c_int, c_void_p],
         "pylon_gemm_tcgen05_force_tile": [c_int],
         "pylon_gemm_tcgen05_qkv_rotate": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_float,
                                           c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
@@ -575,10 +578,11 @@ def linear_stream_partial(x: torch.Tensor, w: torch.Tensor, parts: Optional[int]
     return y
 
 
-def linear_stream(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+def linear_stream(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False, limit: Optional[float] = None, alpha: float = 1.0) -> torch.Tensor:
     """bfloat16 ``x [M <= 64, K] @ w [N, K].T`` on the TMA-fed kernel, one block per 64 weight rows
     over the whole of k; with ``swiglu`` the rows of ``w`` are interleaved gate/up groups (see
-    :func:`interleave_gate_up`) and the result is ``silu(gate) * up``, ``[M, N / 2]``."""
+    :func:`interleave_gate_up`) and the result is ``silu(gate) * up``, ``[M, N / 2]`` - or, with a
+    ``limit``, the clamped gated unit of :func:`swiglu`."""
     _need_cuda(x, w)
     _need(x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1] and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16,
           "linear_stream: bfloat16 x [M, K] and w [N, K]")
@@ -587,6 +591,10 @@ def linear_stream(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> tor
     n = w.shape[0]
     y = torch.empty((m, n // 2 if swiglu else n), dtype=torch.bfloat16, device=x.device)
     library = _library("gemm_stream.cu")
+    if swiglu and limit is not None:
+        _check(library, library.pylon_gemm_stream_glu_clamped(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), y.stride(0), float(limit),
+                                                              float(alpha), _ptr(stream_error_word(x.device)), _stream()))
+        return y
     entry = library.pylon_gemm_stream_swiglu if swiglu else library.pylon_gemm_stream_bf16
     _check(library, entry(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), y.stride(0), _ptr(stream_error_word(x.device)), _stream()))
     return y
@@ -621,10 +629,11 @@ def tcgen05_force_tile(columns: int = 0) -> None:
     _library("gemm_tcgen05.cu").pylon_gemm_tcgen05_force_tile(columns)
 
 
-def linear_tcgen05(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+def linear_tcgen05(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False, limit: Optional[float] = None, alpha: float = 1.0) -> torch.Tensor:
     """bfloat16 ``x [M, K] @ w [N, K].T`` on the tcgen05 tensor cores (TMA-fed, accumulators in
     tensor memory).  With ``swiglu`` the rows of ``w`` are interleaved by
-    :func:`interleave_gate_up` and the result is ``silu(gate) * up``, ``[M, N / 2]``."""
+    :func:`interleave_gate_up` and the result is ``silu(gate) * up``, ``[M, N / 2]`` - or, with a
+    ``limit``, the clamped gated unit of :func:`swiglu`."""
     _need_cuda(x, w)
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1],
           "linear_tcgen05: bfloat16 x [M, K] and w [N, K]")
@@ -633,6 +642,10 @@ def linear_tcgen05(x: torch.Tensor, w: torch.Tensor, swiglu: bool = False) -> to
     n = w.shape[0]
     y = torch.empty((m, n // 2 if swiglu else n), dtype=torch.bfloat16, device=x.device)
     library = _library("gemm_tcgen05.cu")
+    if swiglu and limit is not None:
+        _check(library, library.pylon_gemm_tcgen05_glu_clamped(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), y.stride(0), float(limit),
+                                                               float(alpha), _ptr(tcgen05_error_word(x.device)), _multiprocessors(x.device), _stream()))
+        return y
     _check(library, library.pylon_gemm_tcgen05_bf16(_ptr(x), _ptr(w), _ptr(y), m, n, k, x.stride(0), w.stride(0), y.stride(0), int(swiglu),
                                                     _ptr(tcgen05_error_word(x.device)), _multiprocessors(x.device), _stream()))
     return y
@@ -713,22 +726,23 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack((gate.reshape(inter // 8, 8, k), up.reshape(inter // 8, 8, k)), dim=1).reshape(2 * inter, k).contiguous()
 
 
-def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor) -> torch.Tensor:
+def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, limit: Optional[float] = None, alpha: float = 1.0) -> torch.Tensor:
     """``silu(x @ gate.T) * (x @ up.T)`` for weights stacked by :func:`interleave_gate_up`:
     one kernel for few rows (the TMA-fed decode kernel) and for many (the tcgen05 kernel), the
-    library product and the SwiGLU kernel in between."""
+    library product and the SwiGLU kernel in between.  With a ``limit`` the gated unit is the clamped
+    one of :func:`swiglu`, in the same kernels."""
     _need_cuda(x, w_interleaved)
     n, k = w_interleaved.shape
     m = x.shape[0]
     if (x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and x.dim() == 2 and m <= STREAM_MAX_ROWS and x.shape[1] == k
             and k % 8 == 0 and n % 16 == 0 and x.stride(1) == 1 and w_interleaved.stride(1) == 1 and x.stride(0) % 8 == 0
             and w_interleaved.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w_interleaved.data_ptr() % 16 == 0):
-        return linear_stream(x, w_interleaved, swiglu=True)
+        return linear_stream(x, w_interleaved, swiglu=True, limit=limit, alpha=alpha)
     if (x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and m >= TCGEN05_MIN_ROWS and k % 8 == 0
             and n % 16 == 0 and x.stride(1) == 1 and w_interleaved.stride(1) == 1 and x.stride(0) % 8 == 0 and w_interleaved.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w_interleaved.data_ptr() % 16 == 0):
-        return linear_tcgen05(x, w_interleaved, swiglu=True)   # many rows: our tcgen05 kernel with SwiGLU in its epilogue
-    return swiglu(linear(x, w_interleaved), interleaved=True)
+        return linear_tcgen05(x, w_interleaved, swiglu=True, limit=limit, alpha=alpha)   # many rows: our tcgen05 kernel with the gated unit in its epilogue
+    return swiglu(linear(x, w_interleaved), interleaved=True, limit=limit, alpha=alpha)
 
 
 # ---------------------------------------------------------------------------------------
@@ -1026,7 +1040,7 @@ def gated_delta_rule(
     """The gated delta rule over the tokens of a step (see ``csrc/delta_rule.cu`` for the equations).
 
     ``proj [T, 2 kv_heads dim + 2 heads vdim + 2 heads]``: the projections of the layer's input with columns
-    ``[q | k | v | gate | a | b]``; ``conv_weight`` float32 ``[channels, taps]`` over the q, k, v columns; ``state`` float32
+    ``[q | k | v | gate | a | b]``; ``conv_weight`` float32 ``[taps, channels]`` over the q, k, v columns (the last tap weighs the current token); ``state`` float32
     ``[slots, heads * dim * vdim + (taps - 1) * channels]``: per request the heads' matrices and the convolution's last
     inputs, read at ``state[slots[row]]`` and advanced in place by the row's tokens; ``a_log``, ``dt_bias`` float32
     ``[heads]``; ``norm_weight`` float32 ``[vdim]``.  Returns ``[T, heads * vdim]`` in ``proj``'s dtype: the read-out,
@@ -1036,9 +1050,9 @@ def gated_delta_rule(
     columns = channels + heads * vdim + 2 * heads
     _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] == columns, f"gated_delta_rule: proj must be [T, {columns}]")
     tokens = proj.shape[0]
-    _need(conv_weight.dtype == torch.float32 and conv_weight.dim() == 2 and conv_weight.shape[0] == channels and conv_weight.is_contiguous(),
-          "gated_delta_rule: conv_weight must be contiguous float32 [channels, taps]")
-    taps = conv_weight.shape[1]
+    _need(conv_weight.dtype == torch.float32 and conv_weight.dim() == 2 and conv_weight.shape[1] == channels and conv_weight.is_contiguous(),
+          "gated_delta_rule: conv_weight must be contiguous float32 [taps, channels]")
+    taps = conv_weight.shape[0]
     _need(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous(), "gated_delta_rule: state must be contiguous float32 [slots, floats]")
     for name, tensor, size in (("a_log", a_log, heads), ("dt_bias", dt_bias, heads), ("norm_weight", norm_weight, vdim)):
         _need(tensor.dtype == torch.float32 and tensor.shape == (size,) and tensor.is_contiguous(), f"gated_delta_rule: {name} must be float32 [{size}]")

@@ -77,7 +77,7 @@ class GatedDeltaRule(Mixer):
         # one product for all six projections: columns [q | k | v | gate | a | b] of its result
         self.w_in = torch.cat([tensors[n[key]] for key in ("q", "k", "v", "gate", "decay", "beta")], dim=0).contiguous()
         self.w_o = tensors[n["o"]].contiguous()
-        self.conv = torch.cat([tensors[n[key]] for key in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
+        self.conv = torch.cat([tensors[n[key]] for key in ("q_conv", "k_conv", "v_conv")], dim=0).t().contiguous()   # [taps, channels]
         self.a_log, self.dt_bias, self.norm = (tensors[n[key]].contiguous() for key in ("a_log", "dt_bias", "norm"))
 
     def weight_bytes(self) -> int:

@@ -40,7 +40,7 @@ class SwiGLU(FeedForward):
         n = self.names
         # gate and up share one product.  In bfloat16 their rows alternate in groups of 8, so that
         # the product's kernel can apply silu(gate) * up itself; otherwise they lie in two halves.
-        self.interleaved = dtype == torch.bfloat16 and self.intermediate % 8 == 0 and self.limit is None
+        self.interleaved = dtype == torch.bfloat16 and self.intermediate % 8 == 0
         if self.interleaved:
             self.w_gate_up = ops.interleave_gate_up(tensors[n["gate"]], tensors[n["up"]])
         else:
@@ -52,7 +52,7 @@ class SwiGLU(FeedForward):
 
     def forward(self, h: torch.Tensor, step: StepView) -> torch.Tensor:
         if self.interleaved:
-            activation = ops.linear_swiglu(h, self.w_gate_up)
+            activation = ops.linear_swiglu(h, self.w_gate_up, limit=self.limit, alpha=self.alpha)
         else:
             activation = ops.swiglu(ops.linear(h, self.w_gate_up), limit=self.limit, alpha=self.alpha)
         return ops.linear_for_residual(activation, self.w_down)

@@ -368,7 +368,7 @@ def test_gated_delta_rule_prefill_and_token_by_token(heads, kv_heads, dim, vdim,
     def run(state, pieces, slots):
         step = step_view([p.shape[0] for p in pieces], [0] * len(pieces), dtype)
         step.slots = torch.tensor(slots, dtype=torch.int32, device=DEVICE)
-        out = ops.gated_delta_rule(on(torch.cat(pieces)), on(conv), state, step.token_row, step.q_start, step.slots, on(a_log), on(dt_bias), on(norm),
+        out = ops.gated_delta_rule(on(torch.cat(pieces)), on(conv.t().contiguous()), state, step.token_row, step.q_start, step.slots, on(a_log), on(dt_bias), on(norm),
                                    heads, kv_heads, dim, vdim, len(pieces), eps)
         return torch.split(out.double().cpu(), [p.shape[0] for p in pieces])
 
@@ -493,3 +493,23 @@ def test_qk_norm_value_mix_and_cache_write(dtype):
             torch.testing.assert_close(k_pages[where, :, position % page].double().cpu(), want_k[token], **tolerance)
             torch.testing.assert_close(v_pages[where, :, position % page].double().cpu(), want_v[token], **tolerance)
             token += 1
+
+
+@pytest.mark.parametrize("rows", [1, 5, 24, 40, 300, 1000])
+def test_clamped_gated_unit_in_the_products(rows):
+    """Gate and up as one product with the clamped unit applied where the product ends: the TMA-fed kernel for few rows, the
+    tcgen05 kernel for many, the library product and the unit's own kernel in between."""
+    from pylon_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(rows)
+    width, inner, limit, alpha = 1024, 208, 1.5, 1.702
+    x = torch.randn(rows, width, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(inner, width, generator=g) * 2 / math.sqrt(width)).to(torch.bfloat16)
+    up = (torch.randn(inner, width, generator=g) * 2 / math.sqrt(width)).to(torch.bfloat16)
+    gc = torch.clamp(x.double() @ gate.double().T, max=limit)
+    uc = torch.clamp(x.double() @ up.double().T, -limit, limit)
+    want = gc * torch.sigmoid(alpha * gc) * (uc + 1)
+    stacked = ops.interleave_gate_up(gate.to(DEVICE), up.to(DEVICE))
+    got = ops.linear_swiglu(x.to(DEVICE), stacked, limit=limit, alpha=alpha)
+    torch.testing.assert_close(got.double().cpu(), want, rtol=3e-2, atol=3e-2)
+    assert float((x.double() @ gate.double().T).max()) > limit      # the clamp was in play

@@ -320,6 +320,13 @@ __global__ void __launch_bounds__(128) delta_recurrence_exact_kernel(const float
     }
     delta_copy_commit();
   };
+  // A warp issues in order, so the two sums of a token - S^T k, which the next token waits for, and the read-out S^T q, which
+  // nothing waits for - are not left one behind the other: the read-out of token t is added up lane by lane beside the first sum
+  // of token t + 1 (from the state as token t left it, before the next decay), and both go through one round of shuffles.
+  float q_before[PER];
+#pragma unroll
+  for (int n = 0; n < PER; ++n) q_before[n] = 0.f;
+  float* o_before = nullptr;   // where the pending read-out goes
   int buffer = 0;
   fetch(begin, 0);
   for (int first = begin; first < end; first += stage_tokens) {
@@ -346,29 +353,39 @@ __global__ void __launch_bounds__(128) delta_recurrence_exact_kernel(const float
       }
       const float v = here[2 * DIM + column];
       const float g = here[2 * DIM + COLS], beta = here[2 * DIM + COLS + 1];
-      float dot[2] = {0.f, 0.f};   // two chains: the sums are chains of dependent steps
+      float dot[2] = {0.f, 0.f}, read[2] = {0.f, 0.f};   // two chains each: the sums are chains of dependent steps
 #pragma unroll
       for (int n = 0; n < PER; ++n) {
+        read[n & 1] = fmaf(s[n], q_before[n], read[n & 1]);
         s[n] *= g;
         dot[n & 1] = fmaf(s[n], k[n], dot[n & 1]);
       }
-      float sum = dot[0] + dot[1];
+      float sum = dot[0] + dot[1], o = read[0] + read[1];
 #pragma unroll
-      for (int offset = P >> 1; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+      for (int offset = P >> 1; offset > 0; offset >>= 1) {
+        sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+        o += __shfl_xor_sync(0xffffffffu, o, offset);
+      }
+      if (o_before != nullptr && live && p == 0) *o_before = o;
       const float w = beta * (v - sum);
-      float read[2] = {0.f, 0.f};
 #pragma unroll
       for (int n = 0; n < PER; ++n) {
         s[n] = fmaf(k[n], w, s[n]);
-        read[n & 1] = fmaf(s[n], q[n], read[n & 1]);
+        q_before[n] = q[n];
       }
-      float o = read[0] + read[1];
-#pragma unroll
-      for (int offset = P >> 1; offset > 0; offset >>= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
-      if (live && p == 0) o_row[(long long)token * heads * vdim] = o;
+      o_before = o_row + (long long)token * heads * vdim;
     }
     __syncthreads();   // the stage is free to be filled again
     buffer ^= 1;
+  }
+  {   // the last token's read-out
+    float read[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < PER; ++n) read[n & 1] = fmaf(s[n], q_before[n], read[n & 1]);
+    float o = read[0] + read[1];
+#pragma unroll
+    for (int offset = P >> 1; offset > 0; offset >>= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
+    if (o_before != nullptr && live && p == 0) *o_before = o;
   }
   if (live) {
 #pragma unroll

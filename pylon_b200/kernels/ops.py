@@ -498,6 +498,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
         return linear_skinny(x, w, out_dtype)   # few rows (decode): our weight-streaming kernel
     if out_dtype == torch.bfloat16:
+        if (m <= STREAM_MAX_ROWS and k >= 1024 and k % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            return linear_stream(x, w)   # 9 to 32 rows over a long k: the TMA-fed kernel is ahead of the library there
         if _tcgen05_fills_the_sms(m, n, _multiprocessors(x.device)) and k % 8 == 0 and n % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 \
                 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
             return linear_tcgen05(x, w)

@@ -66,8 +66,13 @@ CONFIGS = {
         attention_layer(4, 2, 64, 64, 0.125, chunk=64, softcap=10.0, v_mix=True, ff=96),
         attention_layer(2, 2, 64, 32, 0.125, chunk=48, softcap=10.0, ff=96),
     ]},
+    # no attention at all: no page is ever held, the state slots are all a request has
+    "delta_only": {"architecture": "Vopepel", "vocab": 45, "width": 32, "norm": {"eps": 1e-5}, "residual_mult": 0.9, "streams": 2, "layers": [
+        delta_layer(2, 1, 32, 16, 3, ff=48),
+        delta_layer(4, 4, 8, 12, 2),
+    ]},
 }
-PAGE_SIZES = {"streams3": 8, "plain": 4, "one_stream": 64}
+PAGE_SIZES = {"streams3": 8, "plain": 4, "one_stream": 64, "delta_only": 16}
 
 
 def draw_weights(config, seed):
@@ -166,7 +171,7 @@ def assert_logits(got, want, dtype, what):
 # ---------------------------------------------------------------------------------------
 # whole models under every cutting
 # ---------------------------------------------------------------------------------------
-LENGTHS = {"streams3": (61, 23, 5, 38, 1, 44, 17), "plain": (70, 9, 35, 2, 41), "one_stream": (150, 70, 3, 129)}
+LENGTHS = {"streams3": (61, 23, 5, 38, 1, 44, 17), "plain": (70, 9, 35, 2, 41), "one_stream": (150, 70, 3, 129), "delta_only": (40, 3, 25, 31, 1)}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -188,6 +193,7 @@ def test_every_cutting_gives_the_plain_logits(models, name, dtype):
         got = trace_tools.run_in_process(engine, steps)
         assert_logits(got, want, dtype, f"{name}, {what}, {dtype}")
         assert engine.cache.free_slots() == 3 and all(group.pool.free_count == group.pool.num_pages for group in engine.cache.groups)
+        assert (len(engine.cache.groups) == 0) == (name == "delta_only")
         del engine
 
 

@@ -66,13 +66,21 @@ CONFIGS = {
         attention_layer(4, 2, 64, 64, 0.125, chunk=64, softcap=10.0, v_mix=True, ff=96),
         attention_layer(2, 2, 64, 32, 0.125, chunk=48, softcap=10.0, ff=96),
     ]},
+    # a width at which the decode steps' products come as partial sums over slices of k and prompts run on the tcgen05 kernels;
+    # values narrower than keys (kept padded in bfloat16) mixed into a layer of another head size; head sizes 64 and 128
+    "wide": {"architecture": "Vopepel", "vocab": 300, "width": 1024, "norm": {"eps": 1e-5}, "residual_mult": 0.6, "streams": 2, "layers": [
+        delta_layer(4, 2, 64, 64, 4, ff=512),
+        attention_layer(8, 4, 64, 32, 0.125, chunk=80, softcap=15.0, v_mix=True, ff=512),
+        attention_layer(4, 4, 32, 32, 0.18, chunk=112, softcap=15.0, v_mix=True),
+        attention_layer(4, 2, 128, 128, 0.09, chunk=200, softcap=25.0, ff=512),
+    ]},
     # no attention at all: no page is ever held, the state slots are all a request has
     "delta_only": {"architecture": "Vopepel", "vocab": 45, "width": 32, "norm": {"eps": 1e-5}, "residual_mult": 0.9, "streams": 2, "layers": [
         delta_layer(2, 1, 32, 16, 3, ff=48),
         delta_layer(4, 4, 8, 12, 2),
     ]},
 }
-PAGE_SIZES = {"streams3": 8, "plain": 4, "one_stream": 64, "delta_only": 16}
+PAGE_SIZES = {"streams3": 8, "plain": 4, "one_stream": 64, "delta_only": 16, "wide": 64}
 
 
 def draw_weights(config, seed):
@@ -171,7 +179,7 @@ def assert_logits(got, want, dtype, what):
 # ---------------------------------------------------------------------------------------
 # whole models under every cutting
 # ---------------------------------------------------------------------------------------
-LENGTHS = {"streams3": (61, 23, 5, 38, 1, 44, 17), "plain": (70, 9, 35, 2, 41), "one_stream": (150, 70, 3, 129), "delta_only": (40, 3, 25, 31, 1)}
+LENGTHS = {"streams3": (61, 23, 5, 38, 1, 44, 17), "plain": (70, 9, 35, 2, 41), "one_stream": (150, 70, 3, 129), "delta_only": (40, 3, 25, 31, 1), "wide": (330, 45, 150)}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

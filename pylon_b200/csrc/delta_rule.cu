@@ -272,7 +272,7 @@ __global__ void delta_recurrence_kernel(const float* __restrict__ qkv, const flo
 }
 
 // The same walk for the sizes models have, with everything that shapes the inner loop known to the compiler: dim = PER * P
-// exactly, P lanes to a column, PER a multiple of 4, 16-byte copies.  A lane holds entries (4 (m P + p) + c) of its column, c < 4,
+// exactly, P lanes to a column (4 to 32), PER a multiple of 4, 16-byte copies.  A lane holds entries (4 (m P + p) + c) of its column, c < 4,
 // m < PER / 4, so that the lanes of a column read a token's keys and queries as neighbouring 16-byte units (no bank conflicts, a
 // quarter of the loads), the shuffles unroll and no access needs a bound.  A token costs some 100 instructions this way; the
 // general kernel above, with its sizes at run time, took 341 (measured at dim 128: 0.33 us a token against 0.48 us).
@@ -353,14 +353,18 @@ __global__ void __launch_bounds__(128) delta_recurrence_exact_kernel(const float
       }
       const float v = here[2 * DIM + column];
       const float g = here[2 * DIM + COLS], beta = here[2 * DIM + COLS + 1];
-      float dot[2] = {0.f, 0.f}, read[2] = {0.f, 0.f};   // two chains each: the sums are chains of dependent steps
+      constexpr int CHAINS = PER >= 16 ? 4 : 2;   // the sums are chains of dependent steps: several side by side
+      float dot[CHAINS], read[CHAINS];
+#pragma unroll
+      for (int c = 0; c < CHAINS; ++c) dot[c] = read[c] = 0.f;
 #pragma unroll
       for (int n = 0; n < PER; ++n) {
-        read[n & 1] = fmaf(s[n], q_before[n], read[n & 1]);
+        read[n % CHAINS] = fmaf(s[n], q_before[n], read[n % CHAINS]);
         s[n] *= g;
-        dot[n & 1] = fmaf(s[n], k[n], dot[n & 1]);
+        dot[n % CHAINS] = fmaf(s[n], k[n], dot[n % CHAINS]);
       }
       float sum = dot[0] + dot[1], o = read[0] + read[1];
+      if (CHAINS == 4) { sum += dot[2] + dot[3]; o += read[2] + read[3]; }
 #pragma unroll
       for (int offset = P >> 1; offset > 0; offset >>= 1) {
         sum += __shfl_xor_sync(0xffffffffu, sum, offset);
@@ -459,8 +463,10 @@ static int launch_delta(const void* proj_v, long long ld, const float* conv_w, i
                        heads, kv_heads, vdim, stage_tokens);                                                                           \
       walked = true;                                                                                                                   \
     }
-    PYLON_DELTA_EXACT(4, 8) PYLON_DELTA_EXACT(8, 8) PYLON_DELTA_EXACT(12, 8) PYLON_DELTA_EXACT(16, 8) PYLON_DELTA_EXACT(12, 16)
-    PYLON_DELTA_EXACT(16, 16) PYLON_DELTA_EXACT(12, 32) PYLON_DELTA_EXACT(16, 32)
+    // lanes to a column: as few as leave a lane 32 entries at most (fewer rounds of shuffles, longer sums per lane: at dim 128 four
+    // lanes of 32 entries took 445 us for 2,048 tokens where eight of 16 took 540)
+    PYLON_DELTA_EXACT(8, 4) PYLON_DELTA_EXACT(16, 4) PYLON_DELTA_EXACT(24, 4) PYLON_DELTA_EXACT(32, 4) PYLON_DELTA_EXACT(20, 8) PYLON_DELTA_EXACT(24, 8)
+    PYLON_DELTA_EXACT(28, 8) PYLON_DELTA_EXACT(32, 8) PYLON_DELTA_EXACT(24, 16) PYLON_DELTA_EXACT(32, 16) PYLON_DELTA_EXACT(32, 32)
 #undef PYLON_DELTA_EXACT
   }
   if (!walked) {

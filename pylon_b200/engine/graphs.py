@@ -99,6 +99,14 @@ class StepGraphs:
             return self.run_padded(entries)
         return None
 
+    def replays_whole(self, entries: Sequence[StepEntry]) -> bool:
+        """Whether ``run`` will replay this step from a graph it has already: the model's kernels are then queued by one
+        launch, all of them or none, so a failure cannot leave a request's state advanced by some layers only."""
+        if not self.decode_only(entries) or len(entries) in self.failed:
+            return False
+        alike = self.step_function.rows_alike(entries) if self.force_alike is None else self.force_alike
+        return len(entries) in (self.captured_alike if alike else self.captured)
+
     # -- capture -----------------------------------------------------------------------------
     def _capture(self, key, step, caches, layout: StepLayout, static_buffer: torch.Tensor, state_of: Sequence[StepEntry]) -> Optional[CapturedStep]:
         from pylon_b200.kernels import ops

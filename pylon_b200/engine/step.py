@@ -248,11 +248,16 @@ class StepFunction:
         self.cache.prepare(batch)          # all pages of the step, or OutOfPages and nothing
         saved_state = None
         try:
-            saved_state = self.cache.save_state([request for request, _ in batch])   # None for models without state
+            # None for models without state; and for a step that replays a captured graph, whose kernels are queued by one
+            # launch or not at all (the copy would cost a decode step as much as reading the states does)
+            if self.graphs is None or not self.graphs.replays_whole(entries):
+                saved_state = self.cache.save_state([request for request, _ in batch])
             logits = None
             if self.graphs is not None:
                 logits = self.graphs.run(entries)
             if logits is None:
+                if saved_state is None:
+                    saved_state = self.cache.save_state([request for request, _ in batch])
                 logits = self._run_eager(entries)
         except BaseException:
             for request, _ in batch:

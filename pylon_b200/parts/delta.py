@@ -29,7 +29,7 @@ from pylon_b200.parts.base import MIXERS, CacheNeed, LayerCache, Mixer, StateNee
 
 @MIXERS.register("gated_delta")
 class GatedDeltaRule(Mixer):
-    takes_padding = False   # the state is found by a token's row; steps of this mixer are never padded
+    takes_padding = True   # the kernels skip tokens without a row and rows without tokens: a padded step leaves no state touched that it should not
 
     def __init__(
         self,

@@ -246,8 +246,9 @@ def test_the_replay_program_runs_the_model(models, tmp_path):
     assert_logits(got, want, "float32", "bin/trace_run")
 
 
+@pytest.mark.parametrize("graphs", [False, True])
 @pytest.mark.parametrize("name", ["streams3", "one_stream"])
-def test_greedy_generation_through_the_scheduler(models, name):
+def test_greedy_generation_through_the_scheduler(models, name, graphs):
     """Several prompts through ``Engine.generate`` with a small prompt budget and few slots: every generated token is the
     arg-max of the plain logits of its own prefix."""
     from pylon_b200.sampling.params import SamplingParams
@@ -255,7 +256,9 @@ def test_greedy_generation_through_the_scheduler(models, name):
     folder, config, weights = models[name]
     prompts = list(make_requests(config, (19, 3, 40, 11, 27, 8), seed=13).values())
     new_tokens = 12
-    engine = engine_for(folder, "float32", PAGE_SIZES[name], 4 * 64, slots=3, prefill_chunk_size=16)
+    # with graphs, decode steps replay at their batch size and steps with prompt portions padded to captured sizes (rows
+    # without tokens, tokens without a row): nothing of the padding may touch a state slot or a page
+    engine = engine_for(folder, "float32", PAGE_SIZES[name], 4 * 64, slots=3, prefill_chunk_size=16, cuda_graphs=graphs)
     results = engine.generate(prompts, SamplingParams(max_new_tokens=new_tokens, temperature=0.0, ignore_eos=True))
     for prompt, result in zip(prompts, results):
         assert len(result.output_ids) == new_tokens
@@ -268,6 +271,9 @@ def test_greedy_generation_through_the_scheduler(models, name):
                 assert float(row[best] - row[sequence[place + 1]]) < 1e-3 * float(row.std()), f"token {place + 1} of a request is not the plain arg-max"
     engine.cache.check()
     assert engine.cache.free_slots() == 3
+    if graphs:
+        replays = engine.step_function.graphs.replays
+        assert replays["decode"] > 0 and replays["padded"] > 0, replays
 
 
 def test_decode_steps_replay_from_cuda_graphs(models):
@@ -363,7 +369,8 @@ def plain_delta_from_projections(proj, conv, a_log, dt_bias, norm, heads, kv_hea
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps", [(4, 2, 16, 24, 4), (1, 1, 100, 5, 1), (3, 3, 64, 64, 3), (2, 1, 200, 40, 8), (8, 2, 128, 128, 4)])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps", [(4, 2, 16, 24, 4), (1, 1, 100, 5, 1), (3, 3, 64, 64, 3), (2, 1, 200, 40, 8), (8, 2, 128, 128, 4),
+                                                         (2, 1, 32, 8, 2), (1, 1, 256, 16, 3), (2, 2, 96, 20, 4), (1, 1, 512, 12, 2)])
 def test_gated_delta_rule_prefill_and_token_by_token(heads, kv_heads, dim, vdim, taps, dtype):
     """Rows of unequal length in one call, then the same sequences cut in portions (two tokens, one token) that continue
     from the state slots; slots in another order than rows; a slot that is used again starts from zero."""

@@ -534,3 +534,59 @@ def test_clamped_gated_unit_in_the_products(rows):
     got = ops.linear_swiglu(x.to(DEVICE), stacked, limit=limit, alpha=alpha)
     torch.testing.assert_close(got.double().cpu(), want, rtol=3e-2, atol=3e-2)
     assert float((x.double() @ gate.double().T).max()) > limit      # the clamp was in play
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim", [(2, 1, 64, 32), (1, 1, 128, 128), (3, 3, 40, 12)])
+def test_the_delta_rule_remembers_a_token_seven_hundred_tokens_back(heads, kv_heads, dim, vdim, dtype):
+    """The inputs are made so that one early token writes a value of its own under a key that no later token touches (every
+    other key is nearly orthogonal to it, the decay is almost one), and the last token asks for exactly that key: its
+    read-out must be that value, through 700 tokens of state - as one prompt, with the last 40 tokens one by one, and in
+    portions of changing size.  A state that is lost or reset anywhere on the way gives another read-out."""
+    from pylon_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(dim)
+    tokens, marked, eps = 700, 3, 1e-5
+    qk, vs = kv_heads * dim, heads * vdim
+    channels = 2 * qk + vs
+    proj = torch.randn(tokens, channels + vs + 2 * heads, generator=g)
+    q_part, k_part, v_part = proj[:, :qk].view(tokens, kv_heads, dim), proj[:, qk : 2 * qk].view(tokens, kv_heads, dim), proj[:, 2 * qk : channels].view(tokens, heads, vdim)
+    k_part[:, :, 0] = -12.0                    # silu(-12) is nothing: no other key has a share of coordinate 0
+    k_part[marked] = -12.0
+    k_part[marked, :, 0] = 12.0                # the marked key is that coordinate alone
+    q_part[-1] = -12.0
+    q_part[-1, :, 0] = 12.0                    # and the last query asks for it
+    pattern = torch.where(torch.arange(vdim) % 3 == 0, 25.0, -25.0)
+    v_part[marked] = pattern
+    proj[:, channels + vs : channels + vs + heads] = 0.0                 # a: with A_log far down the decay is almost one
+    proj[marked, channels + vs + heads :] = 12.0                          # b: the marked token writes with beta near one
+    proj = proj.to(dtype)
+    conv = torch.ones(1, channels)                                        # one tap of weight one: the convolution passes its input on
+    a_log, dt_bias, norm = torch.full((heads,), -14.0), torch.zeros(heads), torch.ones(vdim)
+    want = plain_delta_from_projections(proj, conv.t().contiguous(), a_log, dt_bias, norm, heads, kv_heads, dim, vdim, eps)
+    gate = plain.silu(proj.double()[-1, channels : channels + vs]).view(heads, vdim)
+    recalled = want[-1].view(heads, vdim) / gate                          # the read-out, normalised: the marked value's pattern
+    # (values pass through silu: the pattern arrives as 25 and nothing, and is normalised to root 3 and nothing)
+    assert float(recalled[:, pattern > 0].min()) > 1.5 and float(recalled[:, pattern < 0].abs().max()) < 0.2
+    on = lambda t: t.to(DEVICE)
+    floats = heads * dim * vdim
+    tolerance = dict(rtol=1e-3, atol=1e-3) if dtype == torch.float32 else dict(rtol=4e-2, atol=4e-2)
+
+    def run(portions):
+        state = torch.zeros(2, floats, device=DEVICE)
+        pieces, cursor = [], 0
+        for size in portions:
+            step = step_view([size], [cursor], dtype)
+            step.slots = torch.tensor([1], dtype=torch.int32, device=DEVICE)
+            out = ops.gated_delta_rule(on(proj[cursor : cursor + size].contiguous()), on(conv), state, step.token_row, step.q_start, step.slots,
+                                       on(a_log), on(dt_bias), on(norm), heads, kv_heads, dim, vdim, 1, eps)
+            pieces.append(out.double().cpu())
+            cursor += size
+        assert cursor == tokens
+        return torch.cat(pieces)
+
+    changing = [7, 2, 64, 3, 129, 2, 200, 31, 2, 160, 99, 1]
+    for portions in ([tokens], [tokens - 40] + [1] * 40, changing):
+        got = run(portions)
+        torch.testing.assert_close(got[-1], want[-1], **tolerance)
+        torch.testing.assert_close(got, want, **tolerance)

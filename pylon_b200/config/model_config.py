@@ -296,3 +296,185 @@ class VopepelConfig:
         if self.eos_token_ids:
             data["eos_token_id"] = list(self.eos_token_ids)
         return data
+
+
+# ---------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class RotarySpec:
+    """A rotation of query and key by position: the first ``dims`` elements of a head, frequencies ``base^(-2i / dims)``, and
+    an optional scaling of the frequencies (its parameters as the configuration names them)."""
+
+    dims: int
+    base: float
+    scaling: Optional[tuple[tuple[str, float], ...]] = None   # sorted (name, number) pairs: hashable
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str, scaling_keys: tuple[str, ...]) -> "RotarySpec":
+        dims = _positive_int(data, "dims")
+        if dims % 2:
+            raise ConfigError(f"{where}: rot.dims must be even, got {dims}")
+        scaling = data.get("scaling")
+        pairs = None
+        if scaling is not None:
+            if not isinstance(scaling, dict):
+                raise ConfigError(f"{where}: rot.scaling must be an object or null")
+            pairs = tuple((key, _number(scaling, key)) for key in sorted(scaling_keys))
+        return cls(dims=dims, base=_number(data, "base"), scaling=pairs)
+
+    def to_dict(self) -> dict[str, Any]:
+        return {"dims": self.dims, "base": self.base, "scaling": None if self.scaling is None else dict(self.scaling)}
+
+
+@dataclass(frozen=True)
+class FikeraxLayer:
+    """One layer of a Fikerax model: its mixer (``lightning``, ``attention`` or ``latent_attention``) with its sizes, and the inner
+    width of its feed-forward (``None``: the layer has none)."""
+
+    kind: str
+    heads: int
+    dim: int
+    vdim: int
+    decay: Optional[tuple[float, ...]] = None   # lightning: one per head
+    kv_heads: Optional[int] = None              # attention
+    rot_dim: Optional[int] = None               # latent attention: rotated query/key elements per head, beside ``dim`` others
+    q_rank: Optional[int] = None                # latent attention: size of the query latent
+    kv_rank: Optional[int] = None               # latent attention: size of the key/value latent
+    scale: Optional[float] = None               # both attentions: factor on the scores
+    window: Optional[int] = None                # both attentions: a token sees itself and the window - 1 tokens before it; None: all
+    rot: Optional[RotarySpec] = None
+    ff: Optional[int] = None
+    ff_kind: str = "dense"
+
+    KINDS: ClassVar[tuple[str, ...]] = ("lightning", "attention", "latent_attention")
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], index: int) -> "FikeraxLayer":
+        where = f"layer {index}"
+        kind = _require(data, "type", str)
+        if kind not in cls.KINDS:
+            raise ConfigError(f"{where}: unknown type {kind!r} ({', '.join(cls.KINDS)})")
+        mixer = _mapping(data, "mixer")
+        fields: dict[str, Any] = dict(kind=kind, heads=_positive_int(mixer, "heads"), dim=_positive_int(mixer, "dim"), vdim=_positive_int(mixer, "vdim"))
+        if kind == "lightning":
+            decay = _require(mixer, "decay", list)
+            if len(decay) != fields["heads"] or any(not isinstance(d, (int, float)) or not 0.0 <= d <= 1.0 for d in decay):
+                raise ConfigError(f"{where}: 'decay' must list one number in [0, 1] per head")
+            fields["decay"] = tuple(float(d) for d in decay)
+        else:
+            fields["scale"] = _number(mixer, "scale")
+            if not fields["scale"] > 0:
+                raise ConfigError(f"{where}: scale must be positive")
+            if mixer.get("mask") is not None:
+                fields["window"] = _positive_int(_mapping(mixer, "mask"), "size")
+            if kind == "attention":
+                fields["kv_heads"] = _positive_int(mixer, "kv_heads")
+                if fields["heads"] % fields["kv_heads"]:
+                    raise ConfigError(f"{where}: {fields['heads']} heads cannot be grouped over {fields['kv_heads']} kv_heads")
+                if mixer.get("rot") is not None:
+                    fields["rot"] = RotarySpec.from_dict(_mapping(mixer, "rot"), where, ("factor", "low", "high", "original"))
+                    if fields["rot"].dims > fields["dim"]:
+                        raise ConfigError(f"{where}: rot.dims {fields['rot'].dims} exceeds the head's dim {fields['dim']}")
+            else:
+                for key in ("rot_dim", "q_rank", "kv_rank"):
+                    fields[key] = _positive_int(mixer, key)
+                if mixer.get("rot") is not None:
+                    fields["rot"] = RotarySpec.from_dict(_mapping(mixer, "rot"), where, ("factor", "original", "fast", "slow"))
+                    if fields["rot"].dims > fields["rot_dim"]:
+                        raise ConfigError(f"{where}: rot.dims {fields['rot'].dims} exceeds rot_dim {fields['rot_dim']}")
+        mlp = data.get("mlp")
+        if mlp is not None:
+            if not isinstance(mlp, dict):
+                raise ConfigError(f"{where}: 'mlp' must be an object or null")
+            fields["ff_kind"] = str(mlp.get("kind", "dense"))
+            if fields["ff_kind"] != "dense":
+                raise ConfigError(f"{where}: feed-forward kind {fields['ff_kind']!r} is not built (dense)")
+            fields["ff"] = _positive_int(mlp, "ff")
+        return cls(**fields)
+
+    def to_dict(self) -> dict[str, Any]:
+        mixer: dict[str, Any] = {"heads": self.heads, "dim": self.dim, "vdim": self.vdim}
+        if self.kind == "lightning":
+            mixer["decay"] = list(self.decay)
+        else:
+            mixer["scale"] = self.scale
+            if self.window is not None:
+                mixer["mask"] = {"size": self.window}
+            if self.rot is not None:
+                mixer["rot"] = self.rot.to_dict()
+            if self.kind == "attention":
+                mixer["kv_heads"] = self.kv_heads
+            else:
+                mixer.update(rot_dim=self.rot_dim, q_rank=self.q_rank, kv_rank=self.kv_rank)
+        return {"type": self.kind, "mixer": mixer, "mlp": None if self.ff is None else {"kind": self.ff_kind, "ff": self.ff}}
+
+
+@dataclass(frozen=True)
+class FikeraxConfig:
+    """Fikerax: a decoder whose layers are, in an order the configuration lists, lightning attention (a decayed linear
+    recurrence), grouped-query attention (biases, partly rotated heads, q and k made unit vectors behind the rotation) and
+    latent attention (one small cached row per token, a sink in the softmax), each over a sliding window where it attends,
+    each with a gated feed-forward or none; RMS norms whose weights are stored around zero; the embedding scaled; and a span
+    of layers ``loop_start .. loop_stop - 1`` that runs ``loop_times`` times in a row, the embedding added again before every
+    pass but the first.
+
+    ``config.json`` names the model by ``"architecture": "Fikerax"``.  Field names follow its keys.
+    """
+
+    architecture: ClassVar[str] = "Fikerax"
+
+    vocab: int
+    width: int
+    layers: tuple[FikeraxLayer, ...]
+    norm_eps: float
+    embedding_scale: float = 1.0
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+    eos_token_ids: tuple[int, ...] = field(default_factory=tuple)
+
+    def __post_init__(self) -> None:
+        if not self.layers:
+            raise ConfigError("a model needs at least one layer")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.norm_eps}")
+        if not 0 <= self.loop_start <= self.loop_stop <= len(self.layers) or self.loop_times < 1:
+            raise ConfigError(f"loop {self.loop_start} .. {self.loop_stop} x {self.loop_times} does not fit {len(self.layers)} layers")
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any]) -> "FikeraxConfig":
+        layers = _require(data, "layers", list)
+        eos = data.get("eos_token_id")
+        loop = data.get("loop")
+        if loop is not None and not isinstance(loop, dict):
+            raise ConfigError("'loop' must be an object or null")
+        embedding = data.get("embedding")
+        return cls(
+            vocab=_positive_int(data, "vocab"),
+            width=_positive_int(data, "width"),
+            layers=tuple(FikeraxLayer.from_dict(layer, index) for index, layer in enumerate(layers)),
+            norm_eps=_number(_mapping(data, "norm"), "eps"),
+            embedding_scale=1.0 if embedding is None else _number(_mapping(data, "embedding"), "scale"),
+            loop_start=0 if loop is None else int(_require(loop, "start", int)),
+            loop_stop=0 if loop is None else int(_require(loop, "stop", int)),
+            loop_times=1 if loop is None else _positive_int(loop, "times"),
+            eos_token_ids=() if eos is None else ((eos,) if isinstance(eos, int) else tuple(int(x) for x in eos)),
+        )
+
+    def to_dict(self) -> dict[str, Any]:
+        data: dict[str, Any] = {
+            "architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+            "embedding": {"scale": self.embedding_scale}, "layers": [layer.to_dict() for layer in self.layers],
+            "loop": {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times}, "norm": {"eps": self.norm_eps},
+        }
+        if self.eos_token_ids:
+            data["eos_token_id"] = list(self.eos_token_ids)
+        return data
+
+    def run_order(self) -> list[tuple[int, bool]]:
+        """(layer, whether the embedding is added before it) for every layer run: the layers before the loop, the loop's span
+        ``loop_times`` times, the rest."""
+        order = [(index, False) for index in range(self.loop_start)]
+        for turn in range(self.loop_times):
+            order += [(index, turn > 0 and index == self.loop_start) for index in range(self.loop_start, self.loop_stop)]
+        order += [(index, False) for index in range(self.loop_stop, len(self.layers))]
+        return order

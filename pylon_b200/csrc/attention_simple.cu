@@ -9,7 +9,11 @@
 // the same request (and j > p - window when a window is given); scale 1/sqrt(head size)
 // unless another is passed; query head h reads KV head h / (nq / nkv).  With `chunk` > 0 a token sees
 // only the keys of its own chunk of positions, j / chunk == p / chunk (chunks count from position 0 of
-// the request); with `softcap` c > 0 a score s becomes c * tanh(s / c) before the softmax.
+// the request); with `softcap` c > 0 a score s becomes c * tanh(s / c) before the softmax.  With `sinks`
+// (one float32 per query head) the softmax's denominator also holds exp(sink): a key without a value
+// whose score is the sink as it stands, neither scaled nor capped.  Key and value rows may lie
+// `k_row_stride` / `v_row_stride` elements apart (0: their own widths), so that the values can be the first
+// `dv` columns of the key rows themselves (one latent row per token, read by every head: nkv = 1).
 //
 // The keys of a token are walked in chunks of 128 positions aligned at position 0, so a
 // token's result depends on its position only, not on how the step was cut or batched.
@@ -25,7 +29,8 @@ __global__ void __launch_bounds__(SIMPLE_THREADS) paged_attention_simple_kernel(
     const T* __restrict__ q, long long q_token_stride, const T* __restrict__ k_pages,
     const T* __restrict__ v_pages, T* __restrict__ out, const int* __restrict__ positions,
     const int* __restrict__ token_row, const int* __restrict__ block_table, int table_width, int page_size,
-    int num_pages, int nq, int nkv, int d, int dv, int window, int chunk, float softcap, float scale) {
+    int num_pages, int nq, int nkv, int d, int dv, int window, int chunk, float softcap, float scale,
+    const float* __restrict__ sinks, long long k_row_stride, long long v_row_stride) {
   extern __shared__ long long shared[];
   long long* offsets = shared;                                      // [128] cache rows of the keys (page, head, slot), -1: none
   float* probs = reinterpret_cast<float*>(offsets + SIMPLE_THREADS);  // [128]
@@ -46,7 +51,8 @@ __global__ void __launch_bounds__(SIMPLE_THREADS) paged_attention_simple_kernel(
   float acc[SIMPLE_MAX_DIMS_PER_THREAD];
 #pragma unroll
   for (int k = 0; k < SIMPLE_MAX_DIMS_PER_THREAD; ++k) acc[k] = 0.f;
-  float running_max = -INFINITY, running_sum = 0.f;
+  // a sink is a key of score sinks[h] and value zero, met before all others
+  float running_max = sinks ? sinks[h] : -INFINITY, running_sum = sinks ? 1.f : 0.f;
   __syncthreads();
 
   for (int c0 = (lo / SIMPLE_THREADS) * SIMPLE_THREADS; c0 <= pos; c0 += SIMPLE_THREADS) {
@@ -57,7 +63,7 @@ __global__ void __launch_bounds__(SIMPLE_THREADS) paged_attention_simple_kernel(
       const int page = table[j / page_size];
       if (page >= 0 && page < num_pages) {
         offset = ((long long)page * nkv + kv_head) * page_size + j % page_size;
-        const T* krow = k_pages + offset * d;
+        const T* krow = k_pages + offset * k_row_stride;
         float dot = 0.f;
         for (int e = 0; e < d; ++e) dot = fmaf(qs[e], to_float<T>(krow[e]), dot);
         score = softcap > 0.f ? softcap * tanhf(dot / softcap) : dot;
@@ -81,7 +87,7 @@ __global__ void __launch_bounds__(SIMPLE_THREADS) paged_attention_simple_kernel(
         float a = acc[k] * rescale;
         for (int i = 0; i < valid; ++i) {
           const long long off = offsets[i];
-          if (off >= 0) a = fmaf(probs[i], to_float<T>(v_pages[off * dv + e]), a);
+          if (off >= 0) a = fmaf(probs[i], to_float<T>(v_pages[off * v_row_stride + e]), a);
         }
         acc[k] = a;
       }
@@ -105,11 +111,14 @@ extern "C" int pylon_paged_attention_simple(const void* q, long long q_token_str
                                             const void* v_pages, void* out, const int* positions,
                                             const int* token_row, const int* block_table, int table_width,
                                             int page_size, int num_pages, int nq, int nkv, int d, int dv, int window,
-                                            int chunk, float softcap, float scale, int num_tokens, int dtype,
+                                            int chunk, float softcap, float scale, const float* sinks,
+                                            long long k_row_stride, long long v_row_stride, int num_tokens, int dtype,
                                             cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  if (d < 1 || d > SIMPLE_THREADS * SIMPLE_MAX_DIMS_PER_THREAD)
-    PYLON_REFUSE("paged_attention_simple: head size %d is outside 1..%d", d, SIMPLE_THREADS * SIMPLE_MAX_DIMS_PER_THREAD);
+  if (d < 1 || d > 2048) PYLON_REFUSE("paged_attention_simple: head size %d is outside 1..2048", d);
+  if (k_row_stride == 0) k_row_stride = d;
+  if (v_row_stride == 0) v_row_stride = dv;
+  if (k_row_stride < d || v_row_stride < dv) PYLON_REFUSE("paged_attention_simple: rows of %d / %d elements cannot lie %lld / %lld apart", d, dv, k_row_stride, v_row_stride);
   if (dv < 1 || dv > SIMPLE_THREADS * SIMPLE_MAX_DIMS_PER_THREAD)
     PYLON_REFUSE("paged_attention_simple: value size %d is outside 1..%d", dv, SIMPLE_THREADS * SIMPLE_MAX_DIMS_PER_THREAD);
   if (chunk < 0 || softcap < 0.f) PYLON_REFUSE("paged_attention_simple: chunk %d, soft cap %f", chunk, softcap);
@@ -122,12 +131,12 @@ extern "C" int pylon_paged_attention_simple(const void* q, long long q_token_str
   if (dtype == PYLON_DTYPE_F32)
     paged_attention_simple_kernel<float><<<grid, SIMPLE_THREADS, smem, stream>>>(
         (const float*)q, q_token_stride, (const float*)k_pages, (const float*)v_pages, (float*)out, positions,
-        token_row, block_table, table_width, page_size, num_pages, nq, nkv, d, dv, window, chunk, softcap, scale);
+        token_row, block_table, table_width, page_size, num_pages, nq, nkv, d, dv, window, chunk, softcap, scale, sinks, k_row_stride, v_row_stride);
   else if (dtype == PYLON_DTYPE_BF16)
     paged_attention_simple_kernel<__nv_bfloat16><<<grid, SIMPLE_THREADS, smem, stream>>>(
         (const __nv_bfloat16*)q, q_token_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
         (__nv_bfloat16*)out, positions, token_row, block_table, table_width, page_size, num_pages, nq, nkv, d, dv,
-        window, chunk, softcap, scale);
+        window, chunk, softcap, scale, sinks, k_row_stride, v_row_stride);
   else
     PYLON_REFUSE("paged_attention_simple: unknown dtype %d", dtype);
   PYLON_CHECK_LAUNCH("paged_attention_simple");

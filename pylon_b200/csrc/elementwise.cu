@@ -16,7 +16,7 @@ namespace pylon {
 // -----------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                    float* __restrict__ out, int width, int vocab, float scale, int copies) {
+                                    float* __restrict__ out, int width, int vocab, float scale, int copies, int accumulate) {
   const int t = blockIdx.x;
   int id = ids[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are validated on the host
@@ -24,7 +24,8 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __rest
   float* dst = out + (size_t)t * copies * width;     // a model with several residual streams starts all of them from the same row
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const float value = to_float<T>(row[i]) * scale;   // scale is 1 for models that take the table as it is: exact
-    for (int c = 0; c < copies; ++c) dst[(size_t)c * width + i] = value;
+    // accumulate: the rows are added to what `out` holds (a model that feeds its embedding into the stream again later on)
+    for (int c = 0; c < copies; ++c) dst[(size_t)c * width + i] = accumulate ? dst[(size_t)c * width + i] + value : value;
   }
 }
 
@@ -737,14 +738,14 @@ extern "C" int pylon_take_tokens(int* ids, const int* source, const int* sampled
 }
 
 extern "C" int pylon_embed_gather(const int* ids, const void* table, float* out, int num_tokens, int width,
-                                  int vocab, int dtype, float scale, int copies, cudaStream_t stream) {
+                                  int vocab, int dtype, float scale, int copies, int accumulate, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (width <= 0 || vocab <= 0 || copies < 1) PYLON_REFUSE("embed_gather: width %d, vocab %d, copies %d", width, vocab, copies);
   const int threads = width >= 1024 ? 256 : 128;
   if (dtype == PYLON_DTYPE_F32)
-    embed_gather_kernel<float><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, width, vocab, scale, copies);
+    embed_gather_kernel<float><<<num_tokens, threads, 0, stream>>>(ids, (const float*)table, out, width, vocab, scale, copies, accumulate);
   else if (dtype == PYLON_DTYPE_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, width, vocab, scale, copies);
+    embed_gather_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, out, width, vocab, scale, copies, accumulate);
   else
     PYLON_REFUSE("embed_gather: unknown dtype %d", dtype);
   PYLON_CHECK_LAUNCH("embed_gather");

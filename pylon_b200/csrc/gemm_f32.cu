@@ -13,7 +13,12 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4x4 ou
 
 __global__ void __launch_bounds__(256) gemm_f32_nt_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                           float* __restrict__ y, int M, int N, int K,
-                                                          long long ldx, long long ldw, long long ldy) {
+                                                          long long ldx, long long ldw, long long ldy,
+                                                          long long batch_x, long long batch_w, long long batch_y) {
+  // blockIdx.z: one of several products of the same shape, whose operands lie batch_x / batch_w / batch_y elements apart
+  x += (size_t)blockIdx.z * batch_x;
+  w += (size_t)blockIdx.z * batch_w;
+  y += (size_t)blockIdx.z * batch_y;
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -71,6 +76,19 @@ extern "C" int pylon_gemm_f32_nt(const float* x, const float* w, float* y, int M
   if (ldx < K || ldw < K || ldy < N) PYLON_REFUSE("gemm_f32: a leading dimension is shorter than its row");
   dim3 grid((N + pylon::BN - 1) / pylon::BN, (M + pylon::BM - 1) / pylon::BM);
   if (grid.y > 65535) PYLON_REFUSE("gemm_f32: M = %d is too large", M);
-  pylon::gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(x, w, y, M, N, K, ldx, ldw, ldy);
+  pylon::gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(x, w, y, M, N, K, ldx, ldw, ldy, 0, 0, 0);
   PYLON_CHECK_LAUNCH("gemm_f32");
+}
+
+// `batch` products of one shape in one launch: y_b[M, N] = x_b[M, K] * W_b[N, K]^T, the operands of product b lying
+// b * batch_x / batch_w / batch_y elements behind the first (a head's slice of a row, say: batch_x = the head's width, ldx = the row's).
+extern "C" int pylon_gemm_f32_nt_batched(const float* x, const float* w, float* y, int M, int N, int K, long long ldx, long long ldw, long long ldy,
+                                         int batch, long long batch_x, long long batch_w, long long batch_y, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (K <= 0) PYLON_REFUSE("gemm_f32_batched: K = %d", K);
+  if (ldx < K || ldw < K || ldy < N) PYLON_REFUSE("gemm_f32_batched: a leading dimension is shorter than its row");
+  dim3 grid((N + pylon::BN - 1) / pylon::BN, (M + pylon::BM - 1) / pylon::BM, batch);
+  if (grid.y > 65535 || batch > 65535) PYLON_REFUSE("gemm_f32_batched: M = %d, batch = %d", M, batch);
+  pylon::gemm_f32_nt_kernel<<<grid, 256, 0, stream>>>(x, w, y, M, N, K, ldx, ldw, ldy, batch_x, batch_w, batch_y);
+  PYLON_CHECK_LAUNCH("gemm_f32_batched");
 }

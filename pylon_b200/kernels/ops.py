@@ -164,7 +164,7 @@ def raise_on_kernel_errors(device: torch.device, queued: bool = False, words: Op
 
 _SIGNATURES = {
     "elementwise.cu": {
-        "pylon_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "pylon_embed_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "pylon_take_tokens": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "pylon_logit_transform": [c_void_p, c_longlong, c_float, c_float, c_void_p],
         "pylon_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_void_p],
@@ -192,6 +192,20 @@ _SIGNATURES = {
     },
     "gemm_f32.cu": {
         "pylon_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
+        "pylon_gemm_f32_nt_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_longlong,
+                                      c_longlong, c_longlong, c_void_p],
+    },
+    "lightning.cu": {
+        "pylon_lightning_attention": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int,
+                                      c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "rotary.cu": {
+        "pylon_qkv_rotate_write": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                                   c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+        "pylon_latent_norm_rotate_write": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int,
+                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+        "pylon_rotate_heads": [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                               c_int, c_int, c_int, c_int, c_void_p],
     },
     "gemm_skinny.cu": {
         "pylon_gemm_skinny_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p],
@@ -215,7 +229,7 @@ _SIGNATURES = {
     "attention_simple.cu": {
         "pylon_paged_attention_simple": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
-                                         c_int, c_int, c_void_p],
+                                         c_void_p, c_longlong, c_longlong, c_int, c_int, c_void_p],
     },
     "attention_mma.cu": {
         "pylon_paged_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -271,9 +285,12 @@ def build_all() -> list[str]:
 # ---------------------------------------------------------------------------------------
 # embedding, norms, residual
 # ---------------------------------------------------------------------------------------
-def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0, copies: int = 1) -> torch.Tensor:
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, scale: float = 1.0, copies: int = 1,
+                 accumulate: bool = False) -> torch.Tensor:
     """float32 ``[T, width]`` rows of ``table`` (``[vocab, width]``) picked by int32 ``ids``, times ``scale``.  With
-    ``copies`` > 1 the result is ``[T, copies, width]``, every copy the same row (a model with several residual streams)."""
+    ``copies`` > 1 the result is ``[T, copies, width]``, every copy the same row (a model with several residual streams).
+    ``accumulate``: the rows are added to what ``out`` holds instead of replacing it."""
+    _need(not accumulate or out is not None, "embed_gather: accumulating needs the tensor to add to")
     _need_cuda(ids, table, out)
     _need(ids.dtype == torch.int32 and ids.dim() == 1 and ids.is_contiguous(), "embed_gather: ids must be contiguous int32 [T]")
     _need(table.dim() == 2 and table.is_contiguous(), "embed_gather: table must be contiguous [vocab, width]")
@@ -283,7 +300,7 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Ten
         out = torch.empty(shape, dtype=torch.float32, device=table.device)
     _need(out.dtype == torch.float32 and out.shape == shape and out.is_contiguous(), "embed_gather: out must be contiguous float32 [T, width] or [T, copies, width]")
     library = _library("elementwise.cu")
-    _check(library, library.pylon_embed_gather(_ptr(ids), _ptr(table), _ptr(out), tokens, width, vocab, _dtype_code(table.dtype), float(scale), int(copies), _stream()))
+    _check(library, library.pylon_embed_gather(_ptr(ids), _ptr(table), _ptr(out), tokens, width, vocab, _dtype_code(table.dtype), float(scale), int(copies), int(bool(accumulate)), _stream()))
     return out
 
 
@@ -797,8 +814,14 @@ def paged_attention(
     rows_alike: bool = False,
     chunk: Optional[int] = None,
     softcap: Optional[float] = None,
+    sinks: Optional[torch.Tensor] = None,
+    values_in_keys: Optional[int] = None,
 ) -> torch.Tensor:
     """Causal attention of every token of a step over its request's pages.
+
+    ``sinks``: float32 ``[nq]``; the softmax's denominator of head h also holds ``exp(sinks[h])``, a key without a
+    value whose score is taken as it stands.  ``values_in_keys`` n (with ``v_pages=None``): the values are the first n
+    columns of the key rows themselves - one latent row per token that every head reads (``nkv`` = 1 then).
 
     ``chunk``: a token sees only the keys of its own chunk of positions (``j // chunk == p // chunk``,
     counted from position 0 of the request).  ``softcap`` c: a scaled score s becomes ``c * tanh(s / c)``.
@@ -827,7 +850,13 @@ def paged_attention(
     else on ``mma.sync``; decoded tokens on their own kernel.  float32, and other head sizes up
     to 512, take the plain kernel.
     """
-    _need_cuda(q, k_pages, v_pages, positions, token_row, q_start, kv_len, block_table, out)
+    _need_cuda(q, k_pages, v_pages, positions, token_row, q_start, kv_len, block_table, out, sinks)
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous()), "paged_attention: sinks must be float32 [nq]")
+    if values_in_keys is not None:
+        _need(v_pages is None and k_pages.dim() == 4 and k_pages.is_contiguous() and 1 <= values_in_keys <= k_pages.shape[3],
+              "paged_attention: values inside the key rows are their first columns, and there are no value pages then")
+        return _latent_attention(q, k_pages, int(values_in_keys), positions, token_row, q_start, kv_len, block_table, nq, max_q, max_kv, window, scale,
+                                 sinks, out, row_tokens)
     _need(k_pages.dim() == 4 and v_pages.dim() == 4 and k_pages.shape[:3] == v_pages.shape[:3] and k_pages.is_contiguous() and v_pages.is_contiguous()
           and k_pages.dtype == v_pages.dtype, "paged_attention: pages must be contiguous [P, nkv, page_size, d] and [P, nkv, page_size, value width]")
     num_pages, nkv, page_size, d = k_pages.shape
@@ -849,7 +878,7 @@ def paged_attention(
     _need(out.shape == (tokens, nq * dv) and out.dtype == q.dtype and out.is_contiguous(), "paged_attention: out has the wrong shape or dtype")
     scale = 1.0 / math.sqrt(d) if scale is None else float(scale)
     _need(scale > 0, "paged_attention: the softmax scale must be positive")
-    if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and not force_simple and same_width:
+    if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and not force_simple and same_width and sinks is None:
         library = _library("attention_mma.cu", {"PYLON_HEAD_DIM": d})
         group = nq // nkv
         any_large = max_q * group > 16
@@ -894,12 +923,34 @@ def paged_attention(
             scale, rows, tokens,
             int(max_q), splits, blocks, int(use_tcgen05), int(bool(rows_alike)), _ptr(attention_error_word(q.device)), _stream()))
         return out
-    _need(d <= 512 and dv <= 512, f"paged_attention: head sizes {d} / {dv}: at most 512")
+    _need(d <= 2048 and dv <= 512, f"paged_attention: head sizes {d} / {dv}: at most 2048 / 512")
     library = _library("attention_simple.cu")
     _check(library, library.pylon_paged_attention_simple(
         _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(positions), _ptr(token_row), _ptr(block_table),
-        block_table.shape[1], page_size, num_pages, nq, nkv, d, dv, int(window or 0), int(chunk or 0), float(softcap or 0.0), scale, tokens,
-        _dtype_code(q.dtype), _stream()))
+        block_table.shape[1], page_size, num_pages, nq, nkv, d, dv, int(window or 0), int(chunk or 0), float(softcap or 0.0), scale,
+        _ptr(sinks), 0, 0, tokens, _dtype_code(q.dtype), _stream()))
+    return out
+
+
+def _latent_attention(q, pages, dv, positions, token_row, q_start, kv_len, block_table, nq, max_q, max_kv, window, scale, sinks, out, row_tokens):
+    """Attention of ``nq`` heads over one shared row per token: keys are the whole rows ``[d]``, values their first ``dv`` columns."""
+    num_pages, nkv, page_size, d = pages.shape
+    tokens = q.shape[0]
+    _need(nkv == 1, "paged_attention: a latent row per token is shared by all heads (one KV head)")
+    _need(q.dim() == 2 and q.stride(1) == 1 and q.shape[1] >= nq * d and q.dtype == pages.dtype, "paged_attention: q must be [T, >= nq * d] in the cache dtype")
+    _need(scale is not None and scale > 0, "paged_attention: latent rows need the softmax scale spelled out")
+    for meta in (positions, token_row):
+        _need(meta.dtype == torch.int32 and meta.is_contiguous() and meta.shape[0] >= tokens, "paged_attention: positions/token_row must be int32 [T]")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), "paged_attention: block_table must be contiguous int32 [rows, width]")
+    if out is None:
+        out = torch.empty((tokens, nq * dv), dtype=q.dtype, device=q.device)
+    _need(out.shape == (tokens, nq * dv) and out.dtype == q.dtype and out.is_contiguous(), "paged_attention: out has the wrong shape or dtype")
+    _need(d <= 2048 and dv <= 512, f"paged_attention: latent rows of {d} with values of {dv}: at most 2048 / 512")
+    library = _library("attention_simple.cu")
+    _check(library, library.pylon_paged_attention_simple(
+        _ptr(q), q.stride(0), _ptr(pages), _ptr(pages), _ptr(out), _ptr(positions), _ptr(token_row), _ptr(block_table),
+        block_table.shape[1], page_size, num_pages, nq, 1, d, dv, int(window or 0), 0, 0.0, float(scale),
+        _ptr(sinks), d, d, tokens, _dtype_code(q.dtype), _stream()))
     return out
 
 
@@ -1071,6 +1122,158 @@ def gated_delta_rule(
         _ptr(qkv), _ptr(gates), _ptr(read), _ptr(out), _ptr(a_log), _ptr(dt_bias), _ptr(norm_weight), channels + heads * vdim,
         channels + heads * vdim + heads, channels, heads, kv_heads, dim, vdim, float(unit_eps), float(norm_eps), tokens, num_rows,
         _dtype_code(proj.dtype), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# products per head
+# ---------------------------------------------------------------------------------------
+def linear_heads(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One product per head: ``y[t, h] = w[h] @ x[t, h]`` for ``x [T, H, K]``, ``w [H, N, K]`` -> ``[T, H, N]``.
+
+    ``x`` and ``out`` may be views whose heads are slices of wider rows (any token and head strides; the last dimension
+    contiguous).  float32 runs the plain-FMA kernel, one grid layer per head; bfloat16 goes to the library's batched
+    product with float32 accumulation, as the large plain products do."""
+    _need_cuda(x, w, out)
+    _need(x.dim() == 3 and w.dim() == 3 and x.shape[1] == w.shape[0] and x.shape[2] == w.shape[2], f"linear_heads: shapes {tuple(x.shape)} and {tuple(w.shape)} do not match")
+    _need(x.dtype == w.dtype and x.stride(2) == 1 and w.is_contiguous(), "linear_heads: one dtype, the reduced dimension contiguous, the weights contiguous")
+    tokens, heads, k = x.shape
+    n = w.shape[1]
+    if out is None:
+        out = torch.empty((tokens, heads, n), dtype=x.dtype, device=x.device)
+    _need(out.shape == (tokens, heads, n) and out.dtype == x.dtype and out.stride(2) == 1, "linear_heads: out must be [T, H, N] with its last dimension contiguous")
+    if tokens == 0:
+        return out
+    if x.dtype == torch.float32:
+        library = _library("gemm_f32.cu")
+        _check(library, library.pylon_gemm_f32_nt_batched(_ptr(x), _ptr(w), _ptr(out), tokens, n, k, x.stride(0), k, out.stride(0), heads,
+                                                          x.stride(1), n * k, out.stride(1), _stream()))
+        return out
+    _need(x.dtype == torch.bfloat16, f"linear_heads: unsupported dtype {x.dtype}")
+    torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# rotations, norms and cache writes between an attention mixer's projections and its attention
+# ---------------------------------------------------------------------------------------
+ROTARY_LAYOUTS = {"halves": 0, "neighbours": 1}
+
+
+def _rotary_tables(cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, what: str) -> int:
+    if cos is None:
+        return 0
+    _need(sin is not None and cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.shape == sin.shape and cos.dim() == 2
+          and cos.shape[1] * 2 == rotary_dim and cos.is_contiguous() and sin.is_contiguous(), f"{what}: cos/sin must be float32 [positions, rotary_dim / 2]")
+    return cos.shape[0]
+
+
+def qkv_rotate_write(
+    qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, layout: str,
+    norm: Optional[str], q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float, positions: torch.Tensor,
+    token_row: torch.Tensor, block_table: torch.Tensor, page_size: int, k_pages: torch.Tensor, v_pages: torch.Tensor, nq: int, nkv: int,
+    head_dim: int, value_dim: int,
+) -> torch.Tensor:
+    """On ``qkv [T, nq * d + nkv * d + nkv * dv]``: add ``bias`` (float32, one number per column), rotate the first
+    ``rotary_dim`` elements of every q and k head by the tables (``layout``: ``"halves"`` pairs element i with i + rotary_dim / 2,
+    ``"neighbours"`` element 2 i with 2 i + 1), divide every q and k head by its root mean square (``norm``: ``"before"`` or
+    ``"after"`` the rotation, ``None``: not at all; times ``q_weight`` / ``k_weight [d]`` where given), write q back in place and
+    k, v into the token's slot of its pages ``[pages, nkv, page_size, d]`` and ``[pages, nkv, page_size, dv]``.  Returns ``qkv``."""
+    _need_cuda(qkv, bias, cos, sin, q_weight, k_weight, positions, token_row, block_table, k_pages, v_pages)
+    tokens, columns = qkv.shape[0], nq * head_dim + nkv * head_dim + nkv * value_dim
+    _need(qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] == columns, "qkv_rotate_write: qkv must be [T, nq * d + nkv * d + nkv * dv]")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.shape == (columns,) and bias.is_contiguous()), "qkv_rotate_write: bias must be float32, one per column")
+    _need(layout in ROTARY_LAYOUTS and norm in (None, "before", "after"), f"qkv_rotate_write: layout {layout!r}, norm {norm!r}")
+    table_positions = _rotary_tables(cos, sin, rotary_dim, "qkv_rotate_write")
+    for weight in (q_weight, k_weight):
+        _need(weight is None or (weight.dtype == torch.float32 and weight.shape == (head_dim,) and weight.is_contiguous()), "qkv_rotate_write: norm weights must be float32 [d]")
+    for meta in (positions, token_row):
+        _need(meta.dtype == torch.int32 and meta.is_contiguous() and meta.shape[0] >= tokens, "qkv_rotate_write: positions/token_row must be int32 [T]")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), "qkv_rotate_write: block_table must be contiguous int32 [rows, width]")
+    for pages, width in ((k_pages, head_dim), (v_pages, value_dim)):
+        _need(pages.dtype == qkv.dtype and pages.is_contiguous() and pages.dim() == 4 and pages.shape[1:] == (nkv, page_size, width),
+              "qkv_rotate_write: pages must be contiguous [pages, nkv, page_size, width] in the activation dtype")
+    library = _library("rotary.cu")
+    _check(library, library.pylon_qkv_rotate_write(
+        _ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(cos), _ptr(sin), rotary_dim if cos is not None else 0, ROTARY_LAYOUTS[layout], table_positions,
+        {None: 0, "before": 1, "after": 2}[norm], _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(positions), _ptr(token_row), _ptr(block_table),
+        block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], nq, nkv, head_dim, value_dim, tokens, _dtype_code(qkv.dtype),
+        _ptr(cache_write_error_word(k_pages.device)), _stream()))
+    return qkv
+
+
+def latent_norm_rotate_write(
+    down: torch.Tensor, q_weight: Optional[torch.Tensor], kv_weight: torch.Tensor, eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+    rotary_dim: int, layout: str, positions: torch.Tensor, token_row: torch.Tensor, block_table: torch.Tensor, page_size: int, pages: torch.Tensor,
+    q_rank: int, kv_rank: int, rot_dim: int,
+) -> torch.Tensor:
+    """``down [T, q_rank + kv_rank + rot_dim]``: the query latent, the key/value latent and the rotated key part that all heads
+    share.  Returns the query latent after its RMS norm (times ``q_weight``), ``[T, q_rank]``; the token's one cache row
+    ``[kv_rank + rot_dim]`` in ``pages [pages, 1, page_size, kv_rank + rot_dim]`` receives the key/value latent after its RMS norm
+    (times ``kv_weight``) and the key part with its first ``rotary_dim`` elements rotated (not normed)."""
+    _need_cuda(down, q_weight, kv_weight, cos, sin, positions, token_row, block_table, pages)
+    tokens = down.shape[0]
+    _need(down.dim() == 2 and down.stride(1) == 1 and down.shape[1] == q_rank + kv_rank + rot_dim, "latent_norm_rotate_write: down must be [T, q_rank + kv_rank + rot_dim]")
+    _need(layout in ROTARY_LAYOUTS, f"latent_norm_rotate_write: layout {layout!r}")
+    table_positions = _rotary_tables(cos, sin, rotary_dim, "latent_norm_rotate_write")
+    _need(q_rank == 0 or (q_weight is not None and q_weight.dtype == torch.float32 and q_weight.shape == (q_rank,) and q_weight.is_contiguous()), "latent_norm_rotate_write: q_weight must be float32 [q_rank]")
+    _need(kv_weight.dtype == torch.float32 and kv_weight.shape == (kv_rank,) and kv_weight.is_contiguous(), "latent_norm_rotate_write: kv_weight must be float32 [kv_rank]")
+    for meta in (positions, token_row):
+        _need(meta.dtype == torch.int32 and meta.is_contiguous() and meta.shape[0] >= tokens, "latent_norm_rotate_write: positions/token_row must be int32 [T]")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), "latent_norm_rotate_write: block_table must be contiguous int32 [rows, width]")
+    _need(pages.dtype == down.dtype and pages.is_contiguous() and pages.dim() == 4 and pages.shape[1:] == (1, page_size, kv_rank + rot_dim),
+          "latent_norm_rotate_write: pages must be contiguous [pages, 1, page_size, kv_rank + rot_dim] in the activation dtype")
+    cq = torch.empty((tokens, q_rank), dtype=down.dtype, device=down.device)
+    library = _library("rotary.cu")
+    _check(library, library.pylon_latent_norm_rotate_write(
+        _ptr(down), down.stride(0), _ptr(cq), _ptr(q_weight), _ptr(kv_weight), float(eps), _ptr(cos), _ptr(sin), rotary_dim if cos is not None else 0,
+        ROTARY_LAYOUTS[layout], table_positions, _ptr(positions), _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size, _ptr(pages),
+        pages.shape[0], q_rank, kv_rank, rot_dim, tokens, _dtype_code(down.dtype), _ptr(cache_write_error_word(pages.device)), _stream()))
+    return cq
+
+
+def rotate_heads(src: torch.Tensor, dst: torch.Tensor, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rotary_dim: int, layout: str,
+                 positions: torch.Tensor) -> torch.Tensor:
+    """``dst[t, h] = src[t, h]`` with the first ``rotary_dim`` elements of every head rotated by the token's position.  ``src`` and ``dst``
+    are ``[T, H, width]`` views (any token and head strides, the last dimension contiguous): a slice of each head of a wider row, say."""
+    _need_cuda(src, dst, cos, sin, positions)
+    _need(src.dim() == 3 and src.shape == dst.shape and src.dtype == dst.dtype and src.stride(2) == 1 and dst.stride(2) == 1, "rotate_heads: src and dst must be [T, H, width] views of one dtype")
+    _need(layout in ROTARY_LAYOUTS, f"rotate_heads: layout {layout!r}")
+    table_positions = _rotary_tables(cos, sin, rotary_dim, "rotate_heads")
+    tokens, heads, width = src.shape
+    _need(positions.dtype == torch.int32 and positions.is_contiguous() and positions.shape[0] >= tokens, "rotate_heads: positions must be int32 [T]")
+    library = _library("rotary.cu")
+    _check(library, library.pylon_rotate_heads(
+        _ptr(src), src.stride(0), src.stride(1), _ptr(dst), dst.stride(0), dst.stride(1), _ptr(cos), _ptr(sin), rotary_dim if cos is not None else 0,
+        ROTARY_LAYOUTS[layout], table_positions, _ptr(positions), heads, width, tokens, _dtype_code(src.dtype), _stream()))
+    return dst
+
+
+# ---------------------------------------------------------------------------------------
+# linear attention with a fixed decay per head
+# ---------------------------------------------------------------------------------------
+def lightning_attention(
+    proj: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, decay: torch.Tensor, norm_weight: torch.Tensor,
+    heads: int, dim: int, vdim: int, rows: int, eps: float,
+) -> torch.Tensor:
+    """``proj [T, 2 * heads * dim + 2 * heads * vdim]`` holds the projections ``[q | k | v | gate]`` of a step's tokens.  Per head and
+    request, in token order, in float32: ``S = decay * S + silu(k) silu(v)^T``, ``o = S^T silu(q)``, with S ``[dim, vdim]`` in
+    ``state[slots[row]]`` (``state [slots, heads * dim * vdim]`` float32; a row's tokens are ``q_start[row] .. q_start[row + 1]``).
+    Returns ``o / rms(o) * norm_weight * sigmoid(gate)`` over a token's concatenated heads, ``[T, heads * vdim]`` in the activation dtype."""
+    _need_cuda(proj, state, q_start, slots, decay, norm_weight)
+    tokens, qk, width = proj.shape[0], heads * dim, heads * vdim
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] == 2 * qk + 2 * width, "lightning_attention: proj must be [T, 2 * heads * dim + 2 * heads * vdim]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.shape[1] == qk * vdim and state.is_contiguous(), "lightning_attention: state must be contiguous float32 [slots, heads * dim * vdim]")
+    _need(q_start.dtype == torch.int32 and q_start.is_contiguous() and q_start.shape[0] >= rows + 1, "lightning_attention: q_start must be int32 [rows + 1]")
+    _need(slots.dtype == torch.int32 and slots.is_contiguous() and slots.shape[0] >= rows, "lightning_attention: slots must be int32 [rows]")
+    _need(decay.dtype == torch.float32 and decay.shape == (heads,) and decay.is_contiguous(), "lightning_attention: decay must be float32 [heads]")
+    _need(norm_weight.dtype == torch.float32 and norm_weight.shape == (width,) and norm_weight.is_contiguous(), "lightning_attention: norm_weight must be float32 [heads * vdim]")
+    read_out = torch.empty((tokens, width), dtype=torch.float32, device=proj.device)
+    out = torch.empty((tokens, width), dtype=proj.dtype, device=proj.device)
+    library = _library("lightning.cu")
+    _check(library, library.pylon_lightning_attention(
+        _ptr(proj), proj.stride(0), 0, qk, 2 * qk, 2 * qk + width, _ptr(state), state.stride(0), state.shape[0], _ptr(q_start), _ptr(slots), rows,
+        _ptr(decay), _ptr(norm_weight), float(eps), _ptr(read_out), _ptr(out), tokens, heads, dim, vdim, _dtype_code(proj.dtype), _stream()))
     return out
 
 

@@ -98,6 +98,10 @@ class DecoderModel:
         residual = ops.embed_gather(step.token_ids, self.embedding, scale=self.spec.embedding_scale, copies=self.spec.streams)
         stream = ResidualStream(residual)
         for position, run in enumerate(self.spec.order):
+            if run.add_embedding:
+                stream.flush()   # what the run before left pending joins the sum first; then the embedding rows, in 32-bit like the sum itself
+                ops.embed_gather(step.token_ids, self.embedding, out=stream.residual, scale=self.spec.embedding_scale, copies=self.spec.streams,
+                                 accumulate=True)
             self.blocks[run.layer].forward(stream, step, caches[position])
             if taps is not None:
                 taps.append(stream.total().clone())

@@ -12,6 +12,12 @@ token sees the keys ``j <= i`` with ``j // chunk == i // chunk`` only, chunks co
 0 of the request (``chunk``); and value mixing (``value_mix``): the layer that says ``"source"``
 leaves its values in the step under ``value_mix_key``, a layer that says ``"mix"`` replaces its own
 values by ``(1 - w) v + w v_source`` of the same token, with w a learnt scalar, before they are cached.
+
+And around the rotation: biases on the three projections (``bias``; the tensors' names are the weights' with ``bias_suffix``),
+the per-head norm of q and k behind the rotation instead of before it (``qk_norm="after"``) and without a weight
+(``qk_norm_weight=False``), an encoding that rotates only part of a head or pairs neighbouring elements, and any of these
+together with values of their own width, chunks or a soft cap: one kernel for bias, rotation, norm and cache write
+(``ops.qkv_rotate_write``) then stands between the product and the attention.
 """
 from __future__ import annotations
 
@@ -47,6 +53,10 @@ class GroupedQueryAttention(Mixer):
         softcap: Optional[float] = None,
         value_mix: Optional[str] = None,
         value_mix_key: str = "values",
+        bias: bool = False,
+        bias_suffix: str = ".b",
+        qk_norm: str = "before",
+        qk_norm_weight: bool = True,
     ) -> None:
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads cannot be grouped over {n_kv_heads} KV heads")
@@ -64,6 +74,9 @@ class GroupedQueryAttention(Mixer):
         # the kernels that fuse rotation and cache write take values as wide as the keys and plain causal scores
         self.general = self.value_dim != self.head_dim or self.chunk is not None or self.softcap is not None or value_mix is not None
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        if qk_norm not in ("before", "after"):
+            raise ValueError(f"the q/k norm stands 'before' or 'after' the rotation, not {qk_norm!r}")
+        self.bias, self.bias_suffix, self.qk_norm_place, self.qk_norm_weight = bool(bias), bias_suffix, qk_norm, bool(qk_norm_weight)
         self.window = None if window is None else int(window)
         self.scale = 1.0 / math.sqrt(self.head_dim) if scale is None else float(scale)
         self.position = POSITION_ENCODINGS.build(position) if position is not None else None
@@ -71,8 +84,14 @@ class GroupedQueryAttention(Mixer):
             "q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "value_mix": "vmix", **(names or {}),
         }
-        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.mix_weight = None
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.mix_weight = self.b_qkv = None
         self.kept_value_dim = self.value_dim   # the width values have in the cache: wider than value_dim when they are kept padded
+        # what the kernels that fuse norm, rotation and cache write do not take goes through the kernel that takes everything
+        self.rotary_general = self.bias or self.qk_norm_place == "after" or (self.qk_norm_eps is not None and not self.qk_norm_weight) \
+            or (self.position is not None and (self.general or getattr(self.position, "layout", "halves") != "halves"))
+        if self.rotary_general and (value_mix is not None or (self.position is not None and not hasattr(self.position, "tables"))):
+            raise NotImplementedError("biases, a norm behind the rotation or a rotation beside values of their own width: not with value mixing, and "
+                                      "only with an encoding that rotates by tables of cos and sin")
 
     # -- weights -------------------------------------------------------------------------
     def tensors(self) -> Sequence[TensorDecl]:
@@ -85,13 +104,17 @@ class GroupedQueryAttention(Mixer):
         ]
         if self.value_mix is not None:   # the source layer's weight is in the checkpoint too, and is not used
             decls.append(TensorDecl(n["value_mix"], (), "vector", (0.5, 0.1)))
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             decls += [TensorDecl(n["q_norm"], (self.head_dim,), "vector"), TensorDecl(n["k_norm"], (self.head_dim,), "vector")]
+        if self.bias:
+            decls += [TensorDecl(n[key] + self.bias_suffix, (size,), "vector", (0.0, 0.02))
+                      for key, size in (("q", self.q_size), ("k", self.kv_size), ("v", self.v_size))]
         return decls
 
     def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
         n = self.names
         w_v, w_o = tensors[n["v"]], tensors[n["o"]]
+        b_v = tensors[n["v"] + self.bias_suffix] if self.bias else None
         # The tensor-core attention kernels take values as wide as the keys.  Narrower values are kept padded to the keys'
         # width in bfloat16: zero rows in the value projection, zero columns in the output projection; the padding is zero
         # from the product to the cache and meets zeros in the output product, so nothing else needs to know.
@@ -103,11 +126,17 @@ class GroupedQueryAttention(Mixer):
             padded_o = w_o.new_zeros((self.width, self.n_heads, self.head_dim))
             padded_o[:, :, : self.value_dim] = w_o.view(self.width, self.n_heads, self.value_dim)
             w_v, w_o = padded_v.view(-1, self.width), padded_o.view(self.width, -1)
+            if b_v is not None:
+                padded_b = b_v.new_zeros((self.n_kv_heads, self.head_dim))
+                padded_b[:, : self.value_dim] = b_v.view(self.n_kv_heads, self.value_dim)
+                b_v = padded_b.view(-1)
         # q, k and v share one product: their matrices are stacked by rows at load.
         self.w_qkv = torch.cat((tensors[n["q"]], tensors[n["k"]], w_v), dim=0).contiguous()
         self.w_o = w_o.contiguous()
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             self.q_norm, self.k_norm = tensors[n["q_norm"]].contiguous(), tensors[n["k_norm"]].contiguous()
+        if self.bias:
+            self.b_qkv = torch.cat((tensors[n["q"] + self.bias_suffix], tensors[n["k"] + self.bias_suffix], b_v)).contiguous()
         if self.value_mix == "mix":
             self.mix_weight = tensors[n["value_mix"]].reshape(1).contiguous()
 
@@ -121,6 +150,8 @@ class GroupedQueryAttention(Mixer):
 
     # -- run -----------------------------------------------------------------------------
     def forward(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
+        if self.rotary_general:
+            return self._forward_rotary_general(h, step, cache)
         if self.general:
             return self._forward_general(h, step, cache)
         table = self.position.rotary_table(h.device) if self.position is not None else None
@@ -171,6 +202,23 @@ class GroupedQueryAttention(Mixer):
         )
         if self.value_mix == "source":
             step.carry[self.value_mix_key] = (qkv[:, self.q_size + self.kv_size:], self.kept_value_dim)
+        context = ops.paged_attention(
+            qkv, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
+            self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale, row_tokens=step.row_tokens,
+            rows_alike=step.rows_alike, chunk=self.chunk, softcap=self.softcap,
+        )
+        return ops.linear_for_residual(context, self.w_o)
+
+    def _forward_rotary_general(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
+        """Biases, any rotation by tables, the norm on either side of it, values of any width: the product, one kernel for all of
+        that and the cache write, attention, the output product."""
+        cos, sin, rotary_dim, layout = self.position.tables(h.device) if self.position is not None else (None, None, 0, "halves")
+        qkv = ops.linear(h, self.w_qkv)
+        ops.qkv_rotate_write(
+            qkv, self.b_qkv, cos, sin, rotary_dim, layout, None if self.qk_norm_eps is None else self.qk_norm_place, self.q_norm, self.k_norm,
+            self.qk_norm_eps or 0.0, step.positions, step.token_row, cache.block_table, cache.page_size, cache.k_pages, cache.v_pages,
+            self.n_heads, self.n_kv_heads, self.head_dim, self.kept_value_dim,
+        )
         context = ops.paged_attention(
             qkv, cache.k_pages, cache.v_pages, step.positions, step.token_row, step.q_start, step.kv_len, cache.block_table,
             self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale, row_tokens=step.row_tokens,

@@ -16,18 +16,24 @@ from pylon_b200.parts.base import NORMS, Norm, ResidualStream, TensorDecl
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, width: int, eps: float, weight_name: str = "weight") -> None:
+    """``offset``: the checkpoint stores the weight less this number (a weight kept around zero has ``offset=1``:
+    ``y = x / rms(x) * (1 + w)``); the sum is formed once at load, in float32."""
+
+    def __init__(self, width: int, eps: float, weight_name: str = "weight", offset: float = 0.0) -> None:
         self.width = int(width)
         self.eps = float(eps)
         self.weight_name = weight_name
+        self.offset = float(offset)
         self.weight: Optional[torch.Tensor] = None
         self.dtype: Optional[torch.dtype] = None
 
     def tensors(self) -> Sequence[TensorDecl]:
-        return (TensorDecl(self.weight_name, (self.width,), "vector"),)
+        init = None if self.offset == 0.0 else (1.0 - self.offset, 0.02)
+        return (TensorDecl(self.weight_name, (self.width,), "vector", init),)
 
     def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
-        self.weight = tensors[self.weight_name].contiguous()
+        weight = tensors[self.weight_name]
+        self.weight = (weight if self.offset == 0.0 else weight + self.offset).contiguous()
         self.dtype = dtype
 
     def weight_bytes(self) -> int:

@@ -42,11 +42,15 @@ class RunSpec:
     """One entry of the run order: which layer runs, and whose cache its mixer is handed.
 
     ``cache_of`` is the index of an earlier entry of the order that owns a cache; ``None``
-    means this run owns its own (sized by what its mixer says it needs).
+    means this run owns its own (sized by what its mixer says it needs).  ``add_embedding``: right
+    before this run the step's embedding rows (scaled as they entered the stream) are added to the
+    residual stream once more - what a model does that runs a span of layers several times and feeds
+    its input in again at the start of every further pass.
     """
 
     layer: int
     cache_of: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

@@ -484,7 +484,9 @@ DESIGN_SIZES = {
 }
 DESIGN_CONTEXT = 2_048
 _TIMED_OPS = ("linear", "linear_for_residual", "linear_swiglu", "linear_for_rotation", "linear_qkv_rotated", "paged_attention", "gated_delta_rule",
-              "streams_update_norm", "add_rmsnorm", "swiglu", "qk_norm_mix_kv_write", "qk_norm_rope_kv_write", "embed_gather")
+              "streams_update_norm", "add_rmsnorm", "swiglu", "qk_norm_mix_kv_write", "qk_norm_rope_kv_write", "embed_gather", "lightning_attention",
+              "qkv_rotate_write", "latent_norm_rotate_write", "rotate_heads", "linear_heads")
+DESIGNS = ("vopepel", "qwen3", "fikerax")
 
 
 def vopepel_fields(size: dict) -> dict:
@@ -500,6 +502,27 @@ def vopepel_fields(size: dict) -> dict:
                                                            "mask": {"size": 1_024}, "v_mix": True}}
     return {"architecture": "Vopepel", "vocab": size["vocab"], "width": size["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.5, "streams": 4,
             "layers": [layer(index) for index in range(size["layers"])]}
+
+
+def fikerax_fields(size: dict) -> dict:
+    """A Fikerax model of the given size: of every four layers the first is lightning attention, the third latent attention (a
+    cached row of 512 + 64 numbers per token, the query latent three eighths of the width), the others grouped-query attention
+    with biases; every attention inside a window of 1,024 tokens; no layer runs twice, so that the depth is the other designs'."""
+    def layer(index: int) -> dict:
+        mlp = {"kind": "dense", "ff": size["ff"]}
+        heads, dim = size["heads"], size["head_dim"]
+        if index % 4 == 0:
+            decay = [1.0 - 2.0 ** (-5.0 - 3.0 * head / max(1, heads - 1)) for head in range(heads)]
+            return {"type": "lightning", "mlp": mlp, "mixer": {"heads": heads, "dim": dim, "vdim": dim, "decay": decay}}
+        if index % 4 == 2:
+            return {"type": "latent_attention", "mlp": mlp, "mixer": {
+                "heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "q_rank": size["width"] * 3 // 8, "kv_rank": 512, "scale": (dim + dim // 2) ** -0.5,
+                "mask": {"size": 1_024}, "rot": {"dims": dim // 2, "base": 10_000.0, "scaling": {"factor": 8.0, "original": 4_096, "fast": 32.0, "slow": 1.0}}}}
+        return {"type": "attention", "mlp": mlp, "mixer": {
+            "heads": heads, "kv_heads": size["kv_heads"], "dim": dim, "vdim": dim, "scale": 12.0 / dim, "mask": {"size": 1_024},
+            "rot": {"dims": dim, "base": 500_000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8_192}}}}
+    return {"architecture": "Fikerax", "vocab": size["vocab"], "width": size["width"], "embedding": {"scale": size["width"] ** 0.5}, "norm": {"eps": 1e-5},
+            "loop": {"start": 0, "stop": 0, "times": 1}, "layers": [layer(index) for index in range(size["layers"])]}
 
 
 def qwen3_fields(size: dict) -> dict:
@@ -613,27 +636,29 @@ def time_design(engine, torch, ops, rng, batch: int, steps: int) -> dict:
     return out
 
 
-def run_design_comparison(torch, sizes, batch: int, steps: int) -> dict:
-    """Vopepel and Qwen3 dense at equal width, depth, heads, feed-forward and vocabulary: prefill and decode throughput and
-    the time of every kernel entry point, random weights."""
+def run_design_comparison(torch, sizes, batch: int, steps: int, designs=DESIGNS) -> dict:
+    """Vopepel, Fikerax and Qwen3 dense at equal width, depth, heads, feed-forward and vocabulary: prefill and decode throughput
+    and the time of every kernel entry point, random weights."""
     import gc
 
     import numpy as np
 
     from pylon_b200.config import EngineConfig, Qwen3Config
-    from pylon_b200.config.model_config import VopepelConfig
+    from pylon_b200.config.model_config import FikeraxConfig, VopepelConfig
     from pylon_b200.engine import Engine
     from pylon_b200.kernels import ops
 
     peak = peaks()
-    record = {"metric": "prefill and decode, Vopepel beside Qwen3 at equal size", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
+    made = {"vopepel": lambda size: VopepelConfig.from_dict(vopepel_fields(size)), "qwen3": lambda size: Qwen3Config(**qwen3_fields(size)),
+            "fikerax": lambda size: FikeraxConfig.from_dict(fikerax_fields(size))}
+    record = {"metric": "prefill and decode, " + ", ".join(designs) + " at equal size", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
               "data": "synthetic: random weights, uniform random token ids, caches filled by real prefill",
               "config": {"prefill_tokens": PREFILL_TOKENS, "decode_batch": batch, "decode_context": DESIGN_CONTEXT, "decode_steps": steps,
                          "page_size": PAGE_SIZE, "cuda_graphs": True, "peaks": peak["source"]}, "sizes": {}}
     for name in sizes:
         size = DESIGN_SIZES[name]
         entry = {"size": size}
-        for design, model_config in (("vopepel", VopepelConfig.from_dict(vopepel_fields(size))), ("qwen3", Qwen3Config(**qwen3_fields(size)))):
+        for design, model_config in ((design, made[design](size)) for design in designs):
             config = EngineConfig(dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=(batch + 1) * DESIGN_CONTEXT, max_context=DESIGN_CONTEXT,
                                   max_batch_size=batch + 1, prefill_chunk_size=PREFILL_TOKENS, cuda_graphs=True)
             engine = Engine(None, config, device="cuda:0", model_config=model_config, random_seed=0)
@@ -702,8 +727,9 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
     parser.add_argument("--workload", choices=["decode4b", "mixed8b", "sampled14b", "designs"], default="decode4b",
                         help="decode4b: the headline measurement (default); mixed8b, sampled14b: the serving workloads of the 8B and 14B shapes; "
-                             "designs: Vopepel beside Qwen3 at equal size, prefill and decode with the time of every kernel entry point")
+                             "designs: Vopepel and Fikerax beside Qwen3 at equal size, prefill and decode with the time of every kernel entry point")
     parser.add_argument("--design-sizes", default="2k,4k", help="with --workload designs: which of the sizes 2k, 4k")
+    parser.add_argument("--designs", default=",".join(DESIGNS), help="with --workload designs: which of " + ", ".join(DESIGNS))
     parser.add_argument("--profile", choices=["decode", "prefill"],
                         help="no measurement: run a few steps of this kind between cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     parser.add_argument("--profile-tokens", type=int, default=PREFILL_TOKENS, help="with --profile prefill: tokens of the prompt")
@@ -726,7 +752,10 @@ def main() -> int:
     from pylon_b200.kernels import ops
 
     if args.workload == "designs":
-        print(json.dumps(run_design_comparison(torch, [name for name in args.design_sizes.split(",") if name], args.batch, min(args.steps, 32))))
+        designs = tuple(name for name in args.designs.split(",") if name)
+        if any(name not in DESIGNS for name in designs):
+            parser.error(f"--designs takes {', '.join(DESIGNS)}")
+        print(json.dumps(run_design_comparison(torch, [name for name in args.design_sizes.split(",") if name], args.batch, min(args.steps, 32), designs)))
         return 0
     if args.workload != "decode4b":
         print(json.dumps(run_serving_workload(args.workload, torch)))

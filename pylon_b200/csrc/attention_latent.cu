@@ -1,0 +1,324 @@
+// Paged causal attention over one shared row per token, on the tensor cores (bfloat16, mma.sync m16n8k16).
+//
+// Every query head reads the same cache row of D numbers per token (nkv = 1); the keys are the whole rows, the values their
+// first DV columns.  That is the attention of a mixer that caches a latent per token and applies its per-head key and
+// value matrices on the query's side and behind the attention.  Because the heads share their keys, the heads of a token
+// are packed beside tokens into the M dimension of the products: a block takes 64 packed rows (token-major, then head) of
+// one request - for a decoded token its H heads, for a prompt portion 64 / H tokens - and walks the keys those rows can
+// see in tiles of 32, each tile loaded once for all of them (cp.async, two buffers).
+//
+// Eight warps, 4 along the rows x 2 along the value columns: a warp computes the scores of its 16 rows against the 32
+// keys (both warps of a row pair compute them: nothing is exchanged), does the softmax on them in registers (float32,
+// online, base 2), and adds P V for its half of the value columns, V read from the key tile itself through transposed
+// ldmatrix.  The output accumulator, 16 x DV / 2 per warp, stays in registers.
+//
+// Options: a window (a token at position p sees keys j with p - window < j <= p), sinks (one float32 per head: the
+// softmax's denominator also holds exp(sink), unscaled), and a split of the keys over `splits` blocks per tile for steps
+// with few packed rows (decoded tokens): every block leaves its normalised part, its maximum and its sum in scratch, and
+// a second kernel combines them.  D and DV are compile-time sizes (D a multiple of 16 up to 832, DV a multiple of 32 up to 512).
+#include "common.cuh"
+
+#ifndef PYLON_LATENT_DIM
+#define PYLON_LATENT_DIM 576
+#endif
+#ifndef PYLON_LATENT_VALUE_DIM
+#define PYLON_LATENT_VALUE_DIM 512
+#endif
+
+namespace pylon {
+
+constexpr int LD = PYLON_LATENT_DIM, LDV = PYLON_LATENT_VALUE_DIM;
+constexpr int LAT_BM = 64, LAT_BN = 32, LAT_THREADS = 256;
+constexpr int LAT_PITCH = LD + 8;                 // elements between rows in shared memory: 16 bytes of padding, ldmatrix without bank conflicts
+constexpr int LAT_NV = LDV / 2;                   // value columns of a warp
+constexpr int LAT_NV_TILES = LAT_NV / 8;
+constexpr int LAT_CHUNKS = LD / 8;                // 16-byte chunks of a row
+static_assert(LD % 16 == 0 && LDV % 32 == 0 && LDV <= LD && LDV <= 512 && LD <= 832, "latent attention: rows a multiple of 16 up to 832, values a multiple of 32 up to 512");
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* global, bool valid) {
+  const unsigned address = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;   // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(address), "l"(global), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned address = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned address = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(address));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&pair);
+}
+
+// scratch, when the keys are split: parts [splits, packed rows, LDV] float32, then (maximum, sum) [splits, packed rows, 2];
+// packed row of (token t of the step, head h) = t * nq + h.
+__global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
+    const __nv_bfloat16* __restrict__ q, long long q_stride, const __nv_bfloat16* __restrict__ pages, __nv_bfloat16* __restrict__ out,
+    float* __restrict__ scratch, const int* __restrict__ q_start, const int* __restrict__ kv_len, const int* __restrict__ block_table,
+    int table_width, int page_size, int num_pages, int nq, int window, float scale_log2, const float* __restrict__ sinks, int splits,
+    int total_tokens) {
+  extern __shared__ __align__(16) unsigned char latent_shared[];
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(latent_shared);       // [64][PITCH]
+  __nv_bfloat16* ks = qs + LAT_BM * LAT_PITCH;                                // [2][32][PITCH]
+  const int row = blockIdx.y, tile = blockIdx.x, split = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int wm = warp >> 1, wn = warp & 1;
+  const int t0 = q_start[row], tokens = q_start[row + 1] - t0;
+  const int packed = tokens * nq;
+  if (tile * LAT_BM >= packed) return;   // also a row without tokens
+  const int first_pos = kv_len[row] - tokens;
+  const int* table = block_table + (size_t)row * table_width;
+
+  // the keys the tile's rows can see, in tiles of 32 aligned at position 0
+  const int tok_a = (tile * LAT_BM) / nq;
+  int tok_b = (tile * LAT_BM + LAT_BM - 1) / nq;
+  if (tok_b > tokens - 1) tok_b = tokens - 1;
+  int key_lo = window > 0 ? first_pos + tok_a - window + 1 : 0;
+  if (key_lo < 0) key_lo = 0;
+  const int key_hi = first_pos + tok_b;
+  const int tile_first = key_lo / LAT_BN, tile_last = key_hi / LAT_BN;
+  const int all_tiles = tile_last - tile_first + 1;
+  const int per_split = (all_tiles + splits - 1) / splits;
+  const int my_first = tile_first + split * per_split;
+  int my_last = my_first + per_split - 1;
+  if (my_last > tile_last) my_last = tile_last;
+
+  // the tile's queries
+  for (int c = tid; c < LAT_BM * LAT_CHUNKS; c += LAT_THREADS) {
+    const int m = c / LAT_CHUNKS, part = c % LAT_CHUNKS;
+    const int p = tile * LAT_BM + m;
+    const bool valid = p < packed;
+    const int tok = valid ? p / nq : 0, h = valid ? p % nq : 0;
+    cp_async_16(qs + m * LAT_PITCH + part * 8, q + (size_t)(t0 + tok) * q_stride + (size_t)h * LD + part * 8, valid);
+  }
+  auto load_keys = [&](int key_tile, int buffer) {
+    __nv_bfloat16* dst = ks + (size_t)buffer * LAT_BN * LAT_PITCH;
+    for (int c = tid; c < LAT_BN * LAT_CHUNKS; c += LAT_THREADS) {
+      const int n = c / LAT_CHUNKS, part = c % LAT_CHUNKS;
+      const int j = key_tile * LAT_BN + n;
+      int page = -1;
+      if (j <= key_hi && j / page_size < table_width) page = table[j / page_size];
+      const bool valid = page >= 0 && page < num_pages;
+      const __nv_bfloat16* src = pages + ((size_t)(valid ? page : 0) * page_size + j % page_size) * LD + part * 8;
+      cp_async_16(dst + n * LAT_PITCH + part * 8, src, valid);
+    }
+  };
+  if (my_first <= my_last) load_keys(my_first, 0);
+  cp_async_commit();
+
+  // the two rows of the warp's 16 that this thread holds scores of
+  const int r_lo = wm * 16 + (lane >> 2), r_hi = r_lo + 8;
+  int pos[2], head[2];
+  bool live[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int p = tile * LAT_BM + (i ? r_hi : r_lo);
+    live[i] = p < packed;
+    pos[i] = live[i] ? first_pos + p / nq : -1;
+    head[i] = live[i] ? p % nq : 0;
+  }
+  float top[2], sum[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const bool sink = sinks != nullptr && split == 0 && live[i];   // the sink counts once: in the first part
+    top[i] = sink ? sinks[head[i]] * 1.4426950408889634f : -INFINITY;
+    sum[i] = sink ? 1.f : 0.f;
+  }
+  float o[LAT_NV_TILES][4];
+#pragma unroll
+  for (int n = 0; n < LAT_NV_TILES; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+  for (int key_tile = my_first; key_tile <= my_last; ++key_tile) {
+    const int buffer = (key_tile - my_first) & 1;
+    if (key_tile < my_last) load_keys(key_tile + 1, buffer ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const __nv_bfloat16* kt = ks + (size_t)buffer * LAT_BN * LAT_PITCH;
+
+    // scores of 16 rows x 32 keys
+    float s[4][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll 4
+    for (int k0 = 0; k0 < LD; k0 += 16) {
+      unsigned a[4], b[4];
+      ldmatrix_x4(a, qs + (wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LAT_PITCH + k0 + (lane >> 4) * 8);
+#pragma unroll
+      for (int pair = 0; pair < 2; ++pair) {
+        ldmatrix_x4(b, kt + (pair * 16 + (lane & 7) + (lane >> 4) * 8) * LAT_PITCH + k0 + ((lane >> 3) & 1) * 8);
+        mma_bf16(s[2 * pair], a, b[0], b[1]);
+        mma_bf16(s[2 * pair + 1], a, b[2], b[3]);
+      }
+    }
+    // scale, mask, online softmax in base 2
+    float tile_top[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const int j = key_tile * LAT_BN + n * 8 + (lane & 3) * 2 + (e & 1);
+        const bool seen = live[i] && j <= pos[i] && (window <= 0 || j > pos[i] - window);
+        s[n][e] = seen ? s[n][e] * scale_log2 : -INFINITY;
+        tile_top[i] = fmaxf(tile_top[i], s[n][e]);
+      }
+    }
+    float rescale[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      tile_top[i] = fmaxf(tile_top[i], __shfl_xor_sync(0xffffffffu, tile_top[i], 1));
+      tile_top[i] = fmaxf(tile_top[i], __shfl_xor_sync(0xffffffffu, tile_top[i], 2));
+      const float new_top = fmaxf(top[i], tile_top[i]);
+      rescale[i] = new_top == -INFINITY ? 1.f : exp2f(top[i] - new_top);   // top -inf: nothing was added yet, 0 * anything
+      top[i] = new_top;
+    }
+    float tile_sum[2] = {0.f, 0.f};
+    const float use_top[2] = {top[0] == -INFINITY ? 0.f : top[0], top[1] == -INFINITY ? 0.f : top[1]};
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = e >> 1;
+        const float p = exp2f(s[n][e] - use_top[i]);
+        s[n][e] = p;
+        tile_sum[i] += p;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      tile_sum[i] += __shfl_xor_sync(0xffffffffu, tile_sum[i], 1);
+      tile_sum[i] += __shfl_xor_sync(0xffffffffu, tile_sum[i], 2);
+      sum[i] = sum[i] * rescale[i] + tile_sum[i];
+    }
+#pragma unroll
+    for (int n = 0; n < LAT_NV_TILES; ++n) {
+      o[n][0] *= rescale[0];
+      o[n][1] *= rescale[0];
+      o[n][2] *= rescale[1];
+      o[n][3] *= rescale[1];
+    }
+    // O += P V for the warp's half of the value columns
+#pragma unroll
+    for (int step = 0; step < 2; ++step) {
+      unsigned a[4] = {pack_bf16(s[2 * step][0], s[2 * step][1]), pack_bf16(s[2 * step][2], s[2 * step][3]),
+                       pack_bf16(s[2 * step + 1][0], s[2 * step + 1][1]), pack_bf16(s[2 * step + 1][2], s[2 * step + 1][3])};
+#pragma unroll
+      for (int n = 0; n < LAT_NV_TILES; n += 2) {
+        unsigned b[4];
+        ldmatrix_x4_trans(b, kt + (step * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LAT_PITCH + wn * LAT_NV + n * 8 + (lane >> 4) * 8);
+        mma_bf16(o[n], a, b[0], b[1]);
+        mma_bf16(o[n + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();   // the buffer is free for the tile after next
+  }
+  cp_async_wait<0>();
+
+  // results: straight to the output, or this part to scratch
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    if (!live[i]) continue;
+    const int p = tile * LAT_BM + (i ? r_hi : r_lo);
+    const int token = t0 + p / nq;
+    if (splits == 1) {
+      const float inv = sum[i] > 0.f ? 1.f / sum[i] : 0.f;
+      __nv_bfloat16* dst = out + ((size_t)token * nq + head[i]) * LDV + wn * LAT_NV + (lane & 3) * 2;
+#pragma unroll
+      for (int n = 0; n < LAT_NV_TILES; ++n)
+        *reinterpret_cast<unsigned*>(dst + n * 8) = pack_bf16(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+    } else {
+      const size_t packed_rows = (size_t)total_tokens * nq;
+      const size_t index = (size_t)split * packed_rows + (size_t)token * nq + head[i];
+      const float inv = sum[i] > 0.f ? 1.f / sum[i] : 0.f;
+      float* dst = scratch + index * LDV + wn * LAT_NV + (lane & 3) * 2;
+#pragma unroll
+      for (int n = 0; n < LAT_NV_TILES; ++n) *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+      if (wn == 0 && (lane & 3) == 0) {
+        float* stats = scratch + (size_t)splits * packed_rows * LDV + index * 2;
+        stats[0] = top[i];
+        stats[1] = sum[i];
+      }
+    }
+  }
+}
+
+// out[row] = sum_s w_s part_s[row] / sum_s w_s with w_s = sum_s * 2^(top_s - max top): one block per packed row.
+__global__ void __launch_bounds__(128) latent_attention_combine_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out,
+                                                                      const int* __restrict__ token_row, int nq, int splits, int total_tokens) {
+  const int packed_row = blockIdx.x;
+  if (token_row[packed_row / nq] < 0) return;   // a padding token: no block wrote parts for it
+  const size_t packed_rows = (size_t)total_tokens * nq;
+  const float* stats = scratch + (size_t)splits * packed_rows * LDV;
+  float best = -INFINITY;
+  for (int s = 0; s < splits; ++s) best = fmaxf(best, stats[((size_t)s * packed_rows + packed_row) * 2]);
+  float total = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* st = stats + ((size_t)s * packed_rows + packed_row) * 2;
+    if (st[1] > 0.f) total += st[1] * exp2f(st[0] - best);
+  }
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  for (int e = threadIdx.x; e < LDV; e += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* st = stats + ((size_t)s * packed_rows + packed_row) * 2;
+      if (st[1] > 0.f) acc += st[1] * exp2f(st[0] - best) * scratch[((size_t)s * packed_rows + packed_row) * LDV + e];
+    }
+    out[(size_t)packed_row * LDV + e] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+}  // namespace pylon
+
+using namespace pylon;
+
+extern "C" int pylon_latent_attention_dims(int* d, int* dv) {
+  *d = LD;
+  *dv = LDV;
+  return 0;
+}
+
+// float32 numbers of scratch a call with `splits` > 1 needs.
+extern "C" long long pylon_latent_attention_scratch_floats(int splits, int total_tokens, int nq) {
+  return splits > 1 ? (long long)splits * total_tokens * nq * (LDV + 2) : 0;
+}
+
+extern "C" int pylon_latent_attention(const void* q, long long q_stride, const void* pages, void* out, float* scratch, const int* q_start,
+                                      const int* kv_len, const int* token_row, const int* block_table, int table_width, int page_size, int num_pages,
+                                      int nq, int window, float scale, const float* sinks, int rows, int total_tokens, int max_q, int splits,
+                                      cudaStream_t stream) {
+  if (rows <= 0 || total_tokens <= 0 || max_q <= 0) return 0;
+  if (nq < 1 || page_size < 1 || table_width < 1 || window < 0 || splits < 1 || splits > 65535 || rows > 65535)
+    PYLON_REFUSE("latent_attention: %d heads, page size %d, table width %d, window %d, %d splits, %d rows", nq, page_size, table_width, window, splits, rows);
+  if (q_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)pages & 15)) PYLON_REFUSE("latent_attention: queries and pages must lie on 16-byte boundaries");
+  if (splits > 1 && !scratch) PYLON_REFUSE("latent_attention: %d splits need scratch", splits);
+  const size_t smem = (size_t)(LAT_BM + 2 * LAT_BN) * LAT_PITCH * sizeof(__nv_bfloat16);
+  static bool configured[MAX_DEVICES] = {};
+  bool& done = configured[current_device_slot()];
+  if (!done) {
+    if (cudaFuncSetAttribute(latent_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      PYLON_REFUSE("latent_attention: %zu bytes of shared memory are not to be had", smem);
+    done = true;
+  }
+  const long long tiles = ((long long)max_q * nq + LAT_BM - 1) / LAT_BM;
+  if (tiles > 0x7fffffffLL) PYLON_REFUSE("latent_attention: too many tiles");
+  dim3 grid((unsigned)tiles, rows, splits);
+  latent_attention_kernel<<<grid, LAT_THREADS, smem, stream>>>(
+      (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, (__nv_bfloat16*)out, scratch, q_start, kv_len, block_table, table_width, page_size,
+      num_pages, nq, window, scale * 1.4426950408889634f, sinks, splits, total_tokens);
+  if (splits > 1)
+    latent_attention_combine_kernel<<<(unsigned)((long long)total_tokens * nq), 128, 0, stream>>>(scratch, (__nv_bfloat16*)out, token_row, nq, splits, total_tokens);
+  PYLON_CHECK_LAUNCH("latent_attention");
+}

@@ -195,6 +195,11 @@ _SIGNATURES = {
         "pylon_gemm_f32_nt_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_longlong,
                                       c_longlong, c_longlong, c_void_p],
     },
+    "attention_latent.cu": {
+        "pylon_latent_attention": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                   c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_latent_attention_scratch_floats": [c_int, c_int, c_int],
+    },
     "lightning.cu": {
         "pylon_lightning_attention": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int,
                                       c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -856,7 +861,7 @@ def paged_attention(
         _need(v_pages is None and k_pages.dim() == 4 and k_pages.is_contiguous() and 1 <= values_in_keys <= k_pages.shape[3],
               "paged_attention: values inside the key rows are their first columns, and there are no value pages then")
         return _latent_attention(q, k_pages, int(values_in_keys), positions, token_row, q_start, kv_len, block_table, nq, max_q, max_kv, window, scale,
-                                 sinks, out, row_tokens)
+                                 sinks, out, force_simple, num_splits)
     _need(k_pages.dim() == 4 and v_pages.dim() == 4 and k_pages.shape[:3] == v_pages.shape[:3] and k_pages.is_contiguous() and v_pages.is_contiguous()
           and k_pages.dtype == v_pages.dtype, "paged_attention: pages must be contiguous [P, nkv, page_size, d] and [P, nkv, page_size, value width]")
     num_pages, nkv, page_size, d = k_pages.shape
@@ -932,8 +937,21 @@ def paged_attention(
     return out
 
 
-def _latent_attention(q, pages, dv, positions, token_row, q_start, kv_len, block_table, nq, max_q, max_kv, window, scale, sinks, out, row_tokens):
-    """Attention of ``nq`` heads over one shared row per token: keys are the whole rows ``[d]``, values their first ``dv`` columns."""
+def latent_attention_splits(rows: int, nq: int, max_q: int, max_kv: int, window: Optional[int], sms: int) -> int:
+    """Over how many blocks the tensor-core kernel for latent rows cuts the keys of a tile of 64 packed query rows: one for steps
+    with enough tiles to fill the device (prompt portions); for a few decoded tokens as many as give every SM two blocks, each
+    with at least two key tiles of 32."""
+    tiles = rows * -(-max_q * nq // 64)
+    key_tiles = -(-min(max_kv, (window or max_kv) + max_q) // 32)
+    if max_q * nq > 64 or tiles >= sms or key_tiles < 4:
+        return 1
+    return int(max(1, min(key_tiles // 2, 2 * sms // tiles, 64)))
+
+
+def _latent_attention(q, pages, dv, positions, token_row, q_start, kv_len, block_table, nq, max_q, max_kv, window, scale, sinks, out, force_simple, num_splits):
+    """Attention of ``nq`` heads over one shared row per token: keys are the whole rows ``[d]``, values their first ``dv`` columns.
+    bfloat16 rows of a multiple of 16 numbers (up to 832) with values of a multiple of 32 (up to 512) run on the tensor cores
+    (``csrc/attention_latent.cu``, built per pair of sizes on first use); float32 and other sizes take the plain kernel."""
     num_pages, nkv, page_size, d = pages.shape
     tokens = q.shape[0]
     _need(nkv == 1, "paged_attention: a latent row per token is shared by all heads (one KV head)")
@@ -946,6 +964,19 @@ def _latent_attention(q, pages, dv, positions, token_row, q_start, kv_len, block
         out = torch.empty((tokens, nq * dv), dtype=q.dtype, device=q.device)
     _need(out.shape == (tokens, nq * dv) and out.dtype == q.dtype and out.is_contiguous(), "paged_attention: out has the wrong shape or dtype")
     _need(d <= 2048 and dv <= 512, f"paged_attention: latent rows of {d} with values of {dv}: at most 2048 / 512")
+    rows = block_table.shape[0]
+    _need(q_start.dtype == torch.int32 and q_start.is_contiguous() and q_start.shape[0] >= rows + 1, "paged_attention: q_start must be int32 [rows + 1]")
+    _need(kv_len.dtype == torch.int32 and kv_len.is_contiguous() and kv_len.shape[0] >= rows, "paged_attention: kv_len must be int32 [rows]")
+    if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 832 and dv % 32 == 0 and not force_simple and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
+        library = _library("attention_latent.cu", {"PYLON_LATENT_DIM": d, "PYLON_LATENT_VALUE_DIM": dv})
+        splits = latent_attention_splits(rows, nq, max_q, max_kv, window, _multiprocessors(q.device)) if num_splits is None else int(num_splits)
+        scratch = None
+        if splits > 1:
+            scratch = torch.empty((library.pylon_latent_attention_scratch_floats(splits, tokens, nq),), dtype=torch.float32, device=q.device)
+        _check(library, library.pylon_latent_attention(
+            _ptr(q), q.stride(0), _ptr(pages), _ptr(out), _ptr(scratch), _ptr(q_start), _ptr(kv_len), _ptr(token_row), _ptr(block_table),
+            block_table.shape[1], page_size, num_pages, nq, int(window or 0), float(scale), _ptr(sinks), rows, tokens, int(max_q), splits, _stream()))
+        return out
     library = _library("attention_simple.cu")
     _check(library, library.pylon_paged_attention_simple(
         _ptr(q), q.stride(0), _ptr(pages), _ptr(pages), _ptr(out), _ptr(positions), _ptr(token_row), _ptr(block_table),

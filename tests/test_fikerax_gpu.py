@@ -510,7 +510,8 @@ def test_lightning_attention_reads_back_a_value_written_long_ago():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,rank,rot_dim,window,page", [(3, 16, 8, 13, 4), (1, 36, 4, 2, 8), (8, 128, 32, 150, 64), (5, 64, 16, None, 16)])
+@pytest.mark.parametrize("heads,rank,rot_dim,window,page", [(3, 16, 8, 13, 4), (1, 36, 4, 2, 8), (8, 128, 32, 150, 64), (5, 64, 16, None, 16), (20, 32, 16, 33, 8),
+                                                            (128, 64, 32, 90, 32)])
 def test_attention_over_latent_rows_with_a_sink(heads, rank, rot_dim, window, page, dtype):
     """Every head reads the same row per token, values are the row's first columns, the denominator holds exp(sink); rows of
     unequal length, prompt portions that continue a request beside single tokens, pages shuffled."""
@@ -539,6 +540,12 @@ def test_attention_over_latent_rows_with_a_sink(heads, rank, rot_dim, window, pa
         weights = weights / (weights.sum(dim=-1, keepdim=True) + torch.exp(sinks.double()[:, None, None] - top))
         wants.append(torch.einsum("hij,jv->ihv", weights, keys[:, :rank]).reshape(m, heads * rank))
     torch.testing.assert_close(got.double().cpu(), torch.cat(wants), **tolerance(dtype))
+    # the keys of a tile cut over several blocks whose parts a second kernel combines (the tensor-core kernel's form for a few
+    # decoded tokens), and the plain kernel in the tensor-core kernel's place
+    for options in (dict(num_splits=3), dict(num_splits=7), dict(force_simple=True)):
+        other = ops.paged_attention(on(torch.cat(queries)).view(-1, heads * width), pages, None, step.positions, step.token_row, step.q_start, step.kv_len,
+                                    table, heads, step.max_q, step.max_kv, window=window, scale=scale, sinks=on(sinks), values_in_keys=rank, **options)
+        torch.testing.assert_close(other.double().cpu(), torch.cat(wants), **tolerance(dtype))
     # without the sinks the result differs by far more than the tolerance: the test sees a sink that is left out
     bare = ops.paged_attention(on(torch.cat(queries)).view(-1, heads * width), pages, None, step.positions, step.token_row, step.q_start, step.kv_len,
                                table, heads, step.max_q, step.max_kv, window=window, scale=scale, values_in_keys=rank)

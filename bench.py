@@ -590,8 +590,12 @@ def time_design(engine, torch, ops, rng, batch: int, steps: int) -> dict:
         torch.cuda.synchronize()
         begin.record()
         if timer is not None:
-            with timer:
-                engine.step([StepEntry(request, tokens, (PREFILL_TOKENS - 1,))])
+            graphs, engine.step_function.graphs = engine.step_function.graphs, None     # eager under the timer: a replayed graph calls no entry point
+            try:
+                with timer:
+                    engine.step([StepEntry(request, tokens, (PREFILL_TOKENS - 1,))])
+            finally:
+                engine.step_function.graphs = graphs
         else:
             engine.step([StepEntry(request, tokens, (PREFILL_TOKENS - 1,))])
         end.record()

@@ -202,7 +202,8 @@ _SIGNATURES = {
     },
     "lightning.cu": {
         "pylon_lightning_attention": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int,
-                                      c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                                      c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_lightning_work_floats": [c_int, c_int, c_int, c_int],
     },
     "rotary.cu": {
         "pylon_qkv_rotate_write": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
@@ -1302,9 +1303,10 @@ def lightning_attention(
     read_out = torch.empty((tokens, width), dtype=torch.float32, device=proj.device)
     out = torch.empty((tokens, width), dtype=proj.dtype, device=proj.device)
     library = _library("lightning.cu")
+    work = torch.empty((library.pylon_lightning_work_floats(tokens, heads, dim, vdim),), dtype=torch.float32, device=proj.device)
     _check(library, library.pylon_lightning_attention(
         _ptr(proj), proj.stride(0), 0, qk, 2 * qk, 2 * qk + width, _ptr(state), state.stride(0), state.shape[0], _ptr(q_start), _ptr(slots), rows,
-        _ptr(decay), _ptr(norm_weight), float(eps), _ptr(read_out), _ptr(out), tokens, heads, dim, vdim, _dtype_code(proj.dtype), _stream()))
+        _ptr(decay), _ptr(norm_weight), float(eps), _ptr(read_out), _ptr(work), _ptr(out), tokens, heads, dim, vdim, _dtype_code(proj.dtype), _stream()))
     return out
 
 

@@ -103,18 +103,26 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
     const int tok = valid ? p / nq : 0, h = valid ? p % nq : 0;
     cp_async_16(qs + m * LAT_PITCH + part * 8, q + (size_t)(t0 + tok) * q_stride + (size_t)h * LD + part * 8, valid);
   }
+  // where a tile's 32 keys lie in the pool (element offsets, -1: no such key), looked up once per key by the first threads
+  // a tile ahead of its copy, so that the copy itself is address arithmetic only
+  __shared__ long long key_base[2][LAT_BN];
+  auto find_keys = [&](int key_tile, int which, int n) {
+    const int j = key_tile * LAT_BN + n;
+    int page = -1;
+    if (j <= key_hi && j / page_size < table_width) page = table[j / page_size];
+    key_base[which][n] = page >= 0 && page < num_pages ? ((long long)page * page_size + j % page_size) * LD : -1;
+  };
   auto load_keys = [&](int key_tile, int buffer) {
     __nv_bfloat16* dst = ks + (size_t)buffer * LAT_BN * LAT_PITCH;
+    const long long* base = key_base[key_tile & 1];
     for (int c = tid; c < LAT_BN * LAT_CHUNKS; c += LAT_THREADS) {
       const int n = c / LAT_CHUNKS, part = c % LAT_CHUNKS;
-      const int j = key_tile * LAT_BN + n;
-      int page = -1;
-      if (j <= key_hi && j / page_size < table_width) page = table[j / page_size];
-      const bool valid = page >= 0 && page < num_pages;
-      const __nv_bfloat16* src = pages + ((size_t)(valid ? page : 0) * page_size + j % page_size) * LD + part * 8;
-      cp_async_16(dst + n * LAT_PITCH + part * 8, src, valid);
+      const long long from = base[n];
+      cp_async_16(dst + n * LAT_PITCH + part * 8, pages + (from >= 0 ? from : 0) + part * 8, from >= 0);
     }
   };
+  if (tid < 2 * LAT_BN) find_keys(my_first + tid / LAT_BN, (my_first + tid / LAT_BN) & 1, tid % LAT_BN);
+  __syncthreads();
   if (my_first <= my_last) load_keys(my_first, 0);
   cp_async_commit();
 
@@ -142,25 +150,37 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
 
   for (int key_tile = my_first; key_tile <= my_last; ++key_tile) {
     const int buffer = (key_tile - my_first) & 1;
+    cp_async_wait<0>();
+    __syncthreads();   // the tile is here; every warp is done with the tile before, whose buffer the next copy fills
     if (key_tile < my_last) load_keys(key_tile + 1, buffer ^ 1);
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
+    if (tid < LAT_BN && key_tile + 2 <= my_last) find_keys(key_tile + 2, key_tile & 1, tid);   // read by the copy that the next round issues, behind its barrier
     const __nv_bfloat16* kt = ks + (size_t)buffer * LAT_BN * LAT_PITCH;
 
-    // scores of 16 rows x 32 keys
+    // scores of 16 rows x 32 keys; the fragments of step k + 1 are asked for before the products of step k are issued (the
+    // compiler keeps the order of these instructions as written)
     float s[4][4];
 #pragma unroll
     for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
-#pragma unroll 4
-    for (int k0 = 0; k0 < LD; k0 += 16) {
-      unsigned a[4], b[4];
-      ldmatrix_x4(a, qs + (wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LAT_PITCH + k0 + (lane >> 4) * 8);
+    {
+      const __nv_bfloat16* a_from = qs + (wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LAT_PITCH + (lane >> 4) * 8;
+      const __nv_bfloat16* b_from = kt + ((lane & 7) + (lane >> 4) * 8) * LAT_PITCH + ((lane >> 3) & 1) * 8;
+      unsigned a[2][4], b[2][2][4];
+      ldmatrix_x4(a[0], a_from);
+      ldmatrix_x4(b[0][0], b_from);
+      ldmatrix_x4(b[0][1], b_from + 16 * LAT_PITCH);
 #pragma unroll
-      for (int pair = 0; pair < 2; ++pair) {
-        ldmatrix_x4(b, kt + (pair * 16 + (lane & 7) + (lane >> 4) * 8) * LAT_PITCH + k0 + ((lane >> 3) & 1) * 8);
-        mma_bf16(s[2 * pair], a, b[0], b[1]);
-        mma_bf16(s[2 * pair + 1], a, b[2], b[3]);
+      for (int k = 0; k < LD / 16; ++k) {
+        const int now = k & 1, next = now ^ 1;
+        if (k + 1 < LD / 16) {
+          ldmatrix_x4(a[next], a_from + (k + 1) * 16);
+          ldmatrix_x4(b[next][0], b_from + (k + 1) * 16);
+          ldmatrix_x4(b[next][1], b_from + 16 * LAT_PITCH + (k + 1) * 16);
+        }
+        mma_bf16(s[0], a[now], b[now][0][0], b[now][0][1]);
+        mma_bf16(s[1], a[now], b[now][0][2], b[now][0][3]);
+        mma_bf16(s[2], a[now], b[now][1][0], b[now][1][1]);
+        mma_bf16(s[3], a[now], b[now][1][2], b[now][1][3]);
       }
     }
     // scale, mask, online softmax in base 2
@@ -210,20 +230,27 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
       o[n][2] *= rescale[1];
       o[n][3] *= rescale[1];
     }
-    // O += P V for the warp's half of the value columns
+    // O += P V for the warp's half of the value columns, the next pair of value fragments asked for ahead of the products
+    {
+      const __nv_bfloat16* v_from = kt + ((lane & 7) + ((lane >> 3) & 1) * 8) * LAT_PITCH + wn * LAT_NV + (lane >> 4) * 8;
+      unsigned b[2][4];
+      ldmatrix_x4_trans(b[0], v_from);
 #pragma unroll
-    for (int step = 0; step < 2; ++step) {
-      unsigned a[4] = {pack_bf16(s[2 * step][0], s[2 * step][1]), pack_bf16(s[2 * step][2], s[2 * step][3]),
-                       pack_bf16(s[2 * step + 1][0], s[2 * step + 1][1]), pack_bf16(s[2 * step + 1][2], s[2 * step + 1][3])};
+      for (int step = 0; step < 2; ++step) {
+        const unsigned a[4] = {pack_bf16(s[2 * step][0], s[2 * step][1]), pack_bf16(s[2 * step][2], s[2 * step][3]),
+                               pack_bf16(s[2 * step + 1][0], s[2 * step + 1][1]), pack_bf16(s[2 * step + 1][2], s[2 * step + 1][3])};
 #pragma unroll
-      for (int n = 0; n < LAT_NV_TILES; n += 2) {
-        unsigned b[4];
-        ldmatrix_x4_trans(b, kt + (step * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LAT_PITCH + wn * LAT_NV + n * 8 + (lane >> 4) * 8);
-        mma_bf16(o[n], a, b[0], b[1]);
-        mma_bf16(o[n + 1], a, b[2], b[3]);
+        for (int n = 0; n < LAT_NV_TILES; n += 2) {
+          const int now = (step * (LAT_NV_TILES / 2) + (n >> 1)) & 1, next = now ^ 1;   // the fragments' buffers take turns across both steps
+          if (n + 2 < LAT_NV_TILES)
+            ldmatrix_x4_trans(b[next], v_from + step * 16 * LAT_PITCH + (n + 2) * 8);
+          else if (step == 0)
+            ldmatrix_x4_trans(b[next], v_from + 16 * LAT_PITCH);
+          mma_bf16(o[n], a, b[now][0], b[now][1]);
+          mma_bf16(o[n + 1], a, b[now][2], b[now][3]);
+        }
       }
     }
-    __syncthreads();   // the buffer is free for the tile after next
   }
   cp_async_wait<0>();
 

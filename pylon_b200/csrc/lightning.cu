@@ -23,6 +23,12 @@ constexpr int LIGHTNING_MAX_DIM = 512;    // 32 lanes of 16 entries
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 
+__device__ __forceinline__ void lightning_copy_4(void* smem, const void* global, bool valid) {
+  const unsigned address = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 4 : 0;   // 0: the word is filled with zeros
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(address), "l"(global), "r"(bytes));
+}
+
 __device__ __forceinline__ void lightning_copy_16(void* smem, const void* global) {
   const unsigned address = (unsigned)__cvta_generic_to_shared(smem);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(address), "l"(global));
@@ -81,7 +87,8 @@ __global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel
     }
     for (int e = tid; e < count * columns; e += LIGHTNING_THREADS) {
       const int tt = e / columns, c = e % columns;
-      buffer[tt * token_floats + row_floats + c] = first_column + c < vdim ? v[((size_t)(c0 + tt) * heads + head) * vdim + first_column + c] : 0.f;
+      const bool real = first_column + c < vdim;
+      lightning_copy_4(buffer + tt * token_floats + row_floats + c, v + ((size_t)(c0 + tt) * heads + head) * vdim + (real ? first_column + c : 0), real);
     }
   };
   stage(t0, buffers[0]);
@@ -101,6 +108,8 @@ __global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel
     asm volatile("cp.async.wait_group 1;\n" ::);
     __syncthreads();
     const float* buffer = buffers[turn];
+    // unrolled: a token's shuffles and its store overlap the next tokens' products (the state is the only chain from token to token)
+#pragma unroll 4
     for (int tt = 0; tt < count; ++tt) {
       const float* token = buffer + tt * token_floats;
       const float value = token[row_floats + tid / lanes];

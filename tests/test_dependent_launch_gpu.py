@@ -48,7 +48,8 @@ def test_several_portions_in_one_step_with_and_without_dependent_launch(model, t
     results = {}
     for mode in ("1", "0"):
         env = dict(os.environ, PYLON_B200_PDL=mode)
-        results[mode] = trace_tools.run_program(folder, "bfloat16", steps, tmp_path / f"pdl{mode}", max_tokens=sum(-(-n // 64) * 64 for n in LENGTHS), env=env)
+        results[mode] = trace_tools.run_program(folder, "bfloat16", steps, tmp_path / f"pdl{mode}", max_tokens=sum(-(-n // 64) * 64 for n in LENGTHS), env=env,
+                                                 extra_args=("--max-requests", str(len(LENGTHS))))
     for mode, got in results.items():
         for name, logits in got.items():
             rid = name.split(".")[0]

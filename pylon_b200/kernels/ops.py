@@ -202,8 +202,8 @@ _SIGNATURES = {
     },
     "lightning.cu": {
         "pylon_lightning_attention": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int,
-                                      c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
-        "pylon_lightning_work_floats": [c_int, c_int, c_int, c_int],
+                                      c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_lightning_work_floats": [c_int, c_int, c_int, c_int, c_int, c_int, c_int],
     },
     "rotary.cu": {
         "pylon_qkv_rotate_write": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
@@ -1286,12 +1286,14 @@ def rotate_heads(src: torch.Tensor, dst: torch.Tensor, cos: Optional[torch.Tenso
 # ---------------------------------------------------------------------------------------
 def lightning_attention(
     proj: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, decay: torch.Tensor, norm_weight: torch.Tensor,
-    heads: int, dim: int, vdim: int, rows: int, eps: float,
+    heads: int, dim: int, vdim: int, rows: int, eps: float, max_q: Optional[int] = None,
 ) -> torch.Tensor:
     """``proj [T, 2 * heads * dim + 2 * heads * vdim]`` holds the projections ``[q | k | v | gate]`` of a step's tokens.  Per head and
     request, in token order, in float32: ``S = decay * S + silu(k) silu(v)^T``, ``o = S^T silu(q)``, with S ``[dim, vdim]`` in
     ``state[slots[row]]`` (``state [slots, heads * dim * vdim]`` float32; a row's tokens are ``q_start[row] .. q_start[row + 1]``).
-    Returns ``o / rms(o) * norm_weight * sigmoid(gate)`` over a token's concatenated heads, ``[T, heads * vdim]`` in the activation dtype."""
+    Returns ``o / rms(o) * norm_weight * sigmoid(gate)`` over a token's concatenated heads, ``[T, heads * vdim]`` in the activation dtype.
+    ``max_q``: the most tokens a row brings (an upper bound is fine; default: all of them).  In bfloat16 a row of 1,024 tokens or more is
+    walked in segments of 256 side by side, whose states a scan chains and whose tokens a second walk corrects."""
     _need_cuda(proj, state, q_start, slots, decay, norm_weight)
     tokens, qk, width = proj.shape[0], heads * dim, heads * vdim
     _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] == 2 * qk + 2 * width, "lightning_attention: proj must be [T, 2 * heads * dim + 2 * heads * vdim]")
@@ -1303,10 +1305,11 @@ def lightning_attention(
     read_out = torch.empty((tokens, width), dtype=torch.float32, device=proj.device)
     out = torch.empty((tokens, width), dtype=proj.dtype, device=proj.device)
     library = _library("lightning.cu")
-    work = torch.empty((library.pylon_lightning_work_floats(tokens, heads, dim, vdim),), dtype=torch.float32, device=proj.device)
+    max_q = tokens if max_q is None else int(max_q)
+    work = torch.empty((library.pylon_lightning_work_floats(tokens, rows, max_q, heads, dim, vdim, _dtype_code(proj.dtype)),), dtype=torch.float32, device=proj.device)
     _check(library, library.pylon_lightning_attention(
         _ptr(proj), proj.stride(0), 0, qk, 2 * qk, 2 * qk + width, _ptr(state), state.stride(0), state.shape[0], _ptr(q_start), _ptr(slots), rows,
-        _ptr(decay), _ptr(norm_weight), float(eps), _ptr(read_out), _ptr(work), _ptr(out), tokens, heads, dim, vdim, _dtype_code(proj.dtype), _stream()))
+        _ptr(decay), _ptr(norm_weight), float(eps), _ptr(read_out), _ptr(work), _ptr(out), tokens, max_q, heads, dim, vdim, _dtype_code(proj.dtype), _stream()))
     return out
 
 

@@ -63,5 +63,5 @@ class LightningAttention(Mixer):
     def forward(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
         proj = ops.linear(h, self.w_in)
         mixed = ops.lightning_attention(proj, cache.state, step.q_start, step.slots, self.decay, self.norm, self.n_heads, self.head_dim,
-                                        self.value_dim, step.num_rows, self.norm_eps)
+                                        self.value_dim, step.num_rows, self.norm_eps, max_q=step.max_q)
         return ops.linear_for_residual(mixed, self.w_o)

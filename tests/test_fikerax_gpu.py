@@ -473,6 +473,53 @@ def test_lightning_attention_prefill_and_token_by_token(heads, dim, vdim, dtype)
         turn += 1
 
 
+def test_lightning_attention_walks_long_rows_in_segments():
+    """In bfloat16 a row of 1,024 tokens or more is walked in segments side by side (a scan chains their states, a second walk adds
+    what each token reads of the state before its segment): a long row that continues a request, beside a short row and a row of
+    exactly one segment's length more than the threshold, against the plain recurrence; then each request goes on from its slot."""
+    from pylon_b200.kernels import ops
+
+    heads, dim, vdim, eps = 3, 40, 24, 1e-5
+    g = torch.Generator().manual_seed(77)
+    decay = torch.tensor([0.999, 0.9, 1.0])
+    norm_weight = 1 + 0.2 * torch.randn(heads * vdim, generator=g)
+    columns = 2 * heads * dim + 2 * heads * vdim
+    lengths = (50 + 1700 + 9, 2 + 3 + 1, 1280 + 5)          # each request in its portions
+    portions = ((50, 1700, 9), (2, 3, 1), (1280, 5))
+    projs = [(torch.randn(n, columns, generator=g) * 1.2).to(torch.bfloat16) for n in lengths]
+
+    def plain_mixer(proj):
+        p = proj.double()
+        q, k = plain.silu(p[:, : heads * dim]).view(-1, heads, dim), plain.silu(p[:, heads * dim : 2 * heads * dim]).view(-1, heads, dim)
+        v = plain.silu(p[:, 2 * heads * dim : 2 * heads * dim + heads * vdim]).view(-1, heads, vdim)
+        gate = p[:, 2 * heads * dim + heads * vdim :]
+        state = torch.zeros(heads, dim, vdim, dtype=torch.float64)
+        out = torch.zeros(p.shape[0], heads, vdim, dtype=torch.float64)
+        for t in range(p.shape[0]):
+            state = decay.double()[:, None, None] * state + k[t][:, :, None] * v[t][:, None, :]
+            out[t] = torch.einsum("hdv,hd->hv", state, q[t])
+        return plain.rms_unit(out.reshape(-1, heads * vdim), eps) * norm_weight.double() * torch.sigmoid(gate), state
+
+    wants = [plain_mixer(p) for p in projs]
+    state = torch.zeros(4, heads * dim * vdim, device=DEVICE)
+    slots = [3, 0, 1]
+    cursors = [0, 0, 0]
+    for turn in range(3):
+        rows = [r for r in range(3) if turn < len(portions[r])]
+        sizes = [portions[r][turn] for r in rows]
+        step = step_view(sizes, [cursors[r] for r in rows], torch.bfloat16)
+        step.slots = torch.tensor([slots[r] for r in rows], device=DEVICE, dtype=torch.int32)
+        proj = torch.cat([projs[r][cursors[r] : cursors[r] + size] for r, size in zip(rows, sizes)])
+        got = ops.lightning_attention(on(proj), state, step.q_start, step.slots, on(decay), on(norm_weight), heads, dim, vdim, len(rows), eps, max_q=max(sizes))
+        want = torch.cat([wants[r][0][cursors[r] : cursors[r] + size] for r, size in zip(rows, sizes)])
+        torch.testing.assert_close(got.double().cpu(), want, rtol=3e-2, atol=3e-2)
+        for r, size in zip(rows, sizes):
+            cursors[r] += size
+    for r in range(3):
+        final = wants[r][1]
+        torch.testing.assert_close(state[slots[r]].double().cpu().view(heads, dim, vdim), final, rtol=2e-4, atol=2e-4 * float(final.abs().max()))
+
+
 def test_lightning_attention_reads_back_a_value_written_long_ago():
     """With a decay of almost one, the last of 700 tokens must read the value that one early token wrote: its query is that
     token's key, every other key is small.  One prompt; the last 40 tokens one by one; portions."""

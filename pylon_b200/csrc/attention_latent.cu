@@ -285,24 +285,30 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
 // out[row] = sum_s w_s part_s[row] / sum_s w_s with w_s = sum_s * 2^(top_s - max top): one block per packed row.
 __global__ void __launch_bounds__(128) latent_attention_combine_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out,
                                                                       const int* __restrict__ token_row, int nq, int splits, int total_tokens) {
+  __shared__ float weight[65536 / 1024];   // at most 64 splits
+  __shared__ float total_shared;
   const int packed_row = blockIdx.x;
   if (token_row[packed_row / nq] < 0) return;   // a padding token: no block wrote parts for it
   const size_t packed_rows = (size_t)total_tokens * nq;
   const float* stats = scratch + (size_t)splits * packed_rows * LDV;
-  float best = -INFINITY;
-  for (int s = 0; s < splits; ++s) best = fmaxf(best, stats[((size_t)s * packed_rows + packed_row) * 2]);
-  float total = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float* st = stats + ((size_t)s * packed_rows + packed_row) * 2;
-    if (st[1] > 0.f) total += st[1] * exp2f(st[0] - best);
+  if (threadIdx.x < 32) {   // the parts' weights once, by the first warp
+    float top = -INFINITY, sum = 0.f;
+    for (int s = threadIdx.x; s < splits; s += 32) top = fmaxf(top, stats[((size_t)s * packed_rows + packed_row) * 2]);
+    top = warp_max(top);
+    for (int s = threadIdx.x; s < splits; s += 32) {
+      const float* st = stats + ((size_t)s * packed_rows + packed_row) * 2;
+      const float w = st[1] > 0.f ? st[1] * exp2f(st[0] - top) : 0.f;
+      weight[s] = w;
+      sum += w;
+    }
+    sum = warp_sum(sum);
+    if (threadIdx.x == 0) total_shared = sum;
   }
-  const float inv = total > 0.f ? 1.f / total : 0.f;
+  __syncthreads();
+  const float inv = total_shared > 0.f ? 1.f / total_shared : 0.f;
   for (int e = threadIdx.x; e < LDV; e += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float* st = stats + ((size_t)s * packed_rows + packed_row) * 2;
-      if (st[1] > 0.f) acc += st[1] * exp2f(st[0] - best) * scratch[((size_t)s * packed_rows + packed_row) * LDV + e];
-    }
+    for (int s = 0; s < splits; ++s) acc = fmaf(weight[s], scratch[((size_t)s * packed_rows + packed_row) * LDV + e], acc);
     out[(size_t)packed_row * LDV + e] = __float2bfloat16_rn(acc * inv);
   }
 }
@@ -327,7 +333,7 @@ extern "C" int pylon_latent_attention(const void* q, long long q_stride, const v
                                       int nq, int window, float scale, const float* sinks, int rows, int total_tokens, int max_q, int splits,
                                       cudaStream_t stream) {
   if (rows <= 0 || total_tokens <= 0 || max_q <= 0) return 0;
-  if (nq < 1 || page_size < 1 || table_width < 1 || window < 0 || splits < 1 || splits > 65535 || rows > 65535)
+  if (nq < 1 || page_size < 1 || table_width < 1 || window < 0 || splits < 1 || splits > 64 || rows > 65535)
     PYLON_REFUSE("latent_attention: %d heads, page size %d, table width %d, window %d, %d splits, %d rows", nq, page_size, table_width, window, splits, rows);
   if (q_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)pages & 15)) PYLON_REFUSE("latent_attention: queries and pages must lie on 16-byte boundaries");
   if (splits > 1 && !scratch) PYLON_REFUSE("latent_attention: %d splits need scratch", splits);

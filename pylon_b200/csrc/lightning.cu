@@ -1,7 +1,8 @@
 // Linear attention with a fixed decay per head ("lightning attention"), from its projections on.
 //
 // Per head, with q, k [dim] and v [vdim] of a token (silu of the projections, taken here in float32):
-//   S <- decay * S + k v^T        (S [dim, vdim], float32, one per request and head, kept in the request's state slot)
+//   S <- decay * S + k v^T        (S [dim, vdim], float32, one per request and head, kept in the request's state slot,
+//                                  column by column: entry (d, j) at j * dim + d, so that the lanes of a column read whole sectors)
 //   o  = S^T q                    (the read-out sees the token's own write)
 // and then, over the concatenated heads of a token: y = o / sqrt(mean(o^2) + eps) * weight * sigmoid(gate).
 //
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel
 #pragma unroll
   for (int i = 0; i < LIGHTNING_PER_LANE; ++i) {
     const int d = i * lanes + part;
-    s[i] = (live && d < dim && (CARRY || segment == 0)) ? s_head[(size_t)d * vdim + column] : 0.f;   // a later segment's own walk starts from zero
+    s[i] = (live && d < dim && (CARRY || segment == 0)) ? s_head[(size_t)column * dim + d] : 0.f;   // a later segment's own walk starts from zero
   }
   int turn = 0;
   for (int c0 = t0; c0 < t1; c0 += LIGHTNING_TOKENS, turn ^= 1) {
@@ -178,7 +179,7 @@ __global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel
 #pragma unroll
     for (int i = 0; i < LIGHTNING_PER_LANE; ++i) {
       const int d = i * lanes + part;
-      if (d < dim) s_head[(size_t)d * vdim + column] = s[i];
+      if (d < dim) s_head[(size_t)column * dim + d] = s[i];
     }
   }
 }
@@ -239,7 +240,7 @@ __global__ void __launch_bounds__(256) sigmoid_gated_rmsnorm_kernel(const float*
 using namespace pylon;
 
 // proj [T, ld]: the columns [q | k | v | gate] of a token start at q_col, k_col, v_col, gate_col; q and k hold heads x dim
-// numbers, v and gate heads x vdim.  state [num_slots, heads, dim, vdim] float32; rows: q_start [rows + 1], slots [rows].
+// numbers, v and gate heads x vdim.  state [num_slots, heads, vdim, dim] float32 (a head's matrix column by column); rows: q_start [rows + 1], slots [rows].
 // o [T, heads * vdim] float32 scratch; work: float32 scratch of pylon_lightning_work_floats numbers; y [T, heads * vdim] in
 // the activation dtype.
 

@@ -1290,7 +1290,7 @@ def lightning_attention(
 ) -> torch.Tensor:
     """``proj [T, 2 * heads * dim + 2 * heads * vdim]`` holds the projections ``[q | k | v | gate]`` of a step's tokens.  Per head and
     request, in token order, in float32: ``S = decay * S + silu(k) silu(v)^T``, ``o = S^T silu(q)``, with S ``[dim, vdim]`` in
-    ``state[slots[row]]`` (``state [slots, heads * dim * vdim]`` float32; a row's tokens are ``q_start[row] .. q_start[row + 1]``).
+    ``state[slots[row]]`` (``state [slots, heads * vdim * dim]`` float32, a head's matrix stored column by column: entry (d, j) at ``j * dim + d``; a row's tokens are ``q_start[row] .. q_start[row + 1]``).
     Returns ``o / rms(o) * norm_weight * sigmoid(gate)`` over a token's concatenated heads, ``[T, heads * vdim]`` in the activation dtype.
     ``max_q``: the most tokens a row brings (an upper bound is fine; default: all of them).  In bfloat16 a row of 1,024 tokens or more is
     walked in segments of 256 side by side, whose states a scan chains and whose tokens a second walk corrects."""

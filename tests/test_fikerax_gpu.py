@@ -448,7 +448,7 @@ def test_lightning_attention_prefill_and_token_by_token(heads, dim, vdim, dtype)
     tol = tolerance(dtype)
     torch.testing.assert_close(got.double().cpu(), torch.cat([w[0] for w in wants]), **tol)
     for slot, (_, final) in zip(slots, wants):
-        torch.testing.assert_close(state[slot].double().cpu().view(heads, dim, vdim), final, rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(state[slot].double().cpu().view(heads, vdim, dim).transpose(1, 2), final, rtol=1e-4, atol=1e-4)   # kept column by column
     assert bool(torch.isnan(state[1]).all())
     # the same in portions, continuing from other slots, which are used again
     state.zero_()
@@ -517,7 +517,7 @@ def test_lightning_attention_walks_long_rows_in_segments():
             cursors[r] += size
     for r in range(3):
         final = wants[r][1]
-        torch.testing.assert_close(state[slots[r]].double().cpu().view(heads, dim, vdim), final, rtol=2e-4, atol=2e-4 * float(final.abs().max()))
+        torch.testing.assert_close(state[slots[r]].double().cpu().view(heads, vdim, dim).transpose(1, 2), final, rtol=2e-4, atol=2e-4 * float(final.abs().max()))
 
 
 def test_lightning_attention_reads_back_a_value_written_long_ago():

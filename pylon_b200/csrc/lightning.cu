@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_prepare_kernel(co
 // (S_g = decay^len_g S_(g-1) + part_g) and leaves in parts[row, g - 1] the state at the start of segment g; and the walk with
 // CARRY = true adds to every token of a later segment what it reads of that state, decay^(i + 1) S^T q for the segment's token i.
 template <bool CARRY>
-__global__ void __launch_bounds__(LIGHTNING_THREADS) lightning_recurrence_kernel(
+__global__ void __launch_bounds__(LIGHTNING_THREADS, 4) lightning_recurrence_kernel(
     const float* __restrict__ qk, const float* __restrict__ v, float* __restrict__ state, long long slot_stride, const int* __restrict__ q_start,
     const int* __restrict__ slots, int num_slots, const float* __restrict__ decay, float* __restrict__ out, int heads, int dim, int vdim, int lanes,
     int seg_len, int segments, float* __restrict__ parts) {

@@ -413,7 +413,7 @@ class FikeraxConfig:
     """Fikerax: a decoder whose layers are, in an order the configuration lists, lightning attention (a decayed linear
     recurrence), grouped-query attention (biases, partly rotated heads, q and k made unit vectors behind the rotation) and
     latent attention (one small cached row per token, a sink in the softmax), each over a sliding window where it attends,
-    each with a gated feed-forward or none; RMS norms whose weights are stored around zero; the embedding scaled; and a span
+    each with a gated feed-forward or none; RMS norms whose checkpoints hold the weight less one; the embedding scaled; and a span
     of layers ``loop_start .. loop_stop - 1`` that runs ``loop_times`` times in a row, the embedding added again before every
     pass but the first.
 

@@ -17,7 +17,7 @@ from typing import Optional
 from pylon_b200.config.model_config import FikeraxConfig, FikeraxLayer, RotarySpec
 from pylon_b200.parts.spec import LayerSpec, ModelSpec, PartSpec, RunSpec
 
-NORM_OFFSET = 1.0          # the norms' weights are stored around zero
+NORM_OFFSET = 1.0          # a norm multiplies by one plus the tensor the checkpoint holds
 MAX_POSITIONS = 1 << 20    # no learnt table limits a request's length; the rotation tables are cut to the engine's longest context
 
 

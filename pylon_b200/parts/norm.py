@@ -16,7 +16,7 @@ from pylon_b200.parts.base import NORMS, Norm, ResidualStream, TensorDecl
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
-    """``offset``: the checkpoint stores the weight less this number (a weight kept around zero has ``offset=1``:
+    """``offset``: the checkpoint stores the weight less this number (a checkpoint that holds the weight's difference from one has ``offset=1``:
     ``y = x / rms(x) * (1 + w)``); the sum is formed once at load, in float32."""
 
     def __init__(self, width: int, eps: float, weight_name: str = "weight", offset: float = 0.0) -> None:

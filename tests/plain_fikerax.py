@@ -24,7 +24,7 @@ def rms_unit(x: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def offset_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    """The layers' norm: the weight is stored around zero."""
+    """The layers' norm: the unit-RMS vector times one plus the stored tensor."""
     return rms_unit(x, eps) * (1.0 + w)
 
 

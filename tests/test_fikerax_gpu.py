@@ -94,7 +94,7 @@ LENGTHS = {"mix": (61, 23, 5, 38, 1, 44, 17), "plain": (70, 9, 35, 2, 41), "loop
 
 
 def draw_weights(config, seed):
-    """Weights of a made-up model: matrices N(0, 1/in) times a gain, norm weights around zero where the design stores them
+    """Weights of a made-up model: matrices N(0, 1/in) times a gain, norm tensors near zero where the design adds one to them
     so, sinks of both signs, biases that matter."""
     g = torch.Generator().manual_seed(seed)
     rand = lambda *shape: torch.randn(*shape, generator=g)

@@ -156,6 +156,9 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
     cp_async_commit();
     if (tid < LAT_BN && key_tile + 2 <= my_last) find_keys(key_tile + 2, key_tile & 1, tid);   // read by the copy that the next round issues, behind its barrier
     const __nv_bfloat16* kt = ks + (size_t)buffer * LAT_BN * LAT_PITCH;
+    // a warp whose 16 rows lie behind the tile's last packed row (a decoded token of 16 heads fills one warp pair of four) only
+    // helps with the copies and keeps the barriers
+    if (tile * LAT_BM + wm * 16 >= packed) continue;
 
     // scores of 16 rows x 32 keys; the fragments of step k + 1 are asked for before the products of step k are issued (the
     // compiler keeps the order of these instructions as written)

@@ -7,10 +7,10 @@
 // one request - for a decoded token its H heads, for a prompt portion 64 / H tokens - and walks the keys those rows can
 // see in tiles of 32, each tile loaded once for all of them (cp.async, two buffers).
 //
-// Eight warps, 4 along the rows x 2 along the value columns: a warp computes the scores of its 16 rows against the 32
-// keys (both warps of a row pair compute them: nothing is exchanged), does the softmax on them in registers (float32,
-// online, base 2), and adds P V for its half of the value columns, V read from the key tile itself through transposed
-// ldmatrix.  The output accumulator, 16 x DV / 2 per warp, stays in registers.
+// Eight warps, 4 along the rows x 2: the two warps of a row pair each compute the scores of the pair's 16 rows against half
+// of the tile's 32 keys, hand each other the rows' maxima and their halves of the softmax weights (float32, online, base 2;
+// through shared memory, behind a barrier of the pair's own), and each adds P V for its half of the value columns, V read
+// from the key tile itself through transposed ldmatrix.  The output accumulator, 16 x DV / 2 per warp, stays in registers.
 //
 // Options: a window (a token at position p sees keys j with p - window < j <= p), sinks (one float32 per head: the
 // softmax's denominator also holds exp(sink), unscaled), and a split of the keys over `splits` blocks per tile for steps
@@ -106,6 +106,10 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
   // where a tile's 32 keys lie in the pool (element offsets, -1: no such key), looked up once per key by the first threads
   // a tile ahead of its copy, so that the copy itself is address arithmetic only
   __shared__ long long key_base[2][LAT_BN];
+  // what the two warps of a row pair hand each other: their rows' maxima (and, at the end, sums), and their halves of a tile's weights
+  __shared__ float pair_row[4][2][16];
+  __shared__ __align__(16) __nv_bfloat16 pair_weights[4][16][LAT_BN + 8];
+  auto pair_barrier = [](int pair) { asm volatile("bar.sync %0, 64;\n" ::"r"(pair + 1) : "memory"); };
   auto find_keys = [&](int key_tile, int which, int n) {
     const int j = key_tile * LAT_BN + n;
     int page = -1;
@@ -142,7 +146,7 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
   for (int i = 0; i < 2; ++i) {
     const bool sink = sinks != nullptr && split == 0 && live[i];   // the sink counts once: in the first part
     top[i] = sink ? sinks[head[i]] * 1.4426950408889634f : -INFINITY;
-    sum[i] = sink ? 1.f : 0.f;
+    sum[i] = sink && wn == 0 ? 1.f : 0.f;   // a row's sum is kept in two halves, one per warp of the pair; the sink's one is in the first
   }
   float o[LAT_NV_TILES][4];
 #pragma unroll
@@ -160,65 +164,69 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
     // helps with the copies and keeps the barriers
     if (tile * LAT_BM + wm * 16 >= packed) continue;
 
-    // scores of 16 rows x 32 keys; the fragments of step k + 1 are asked for before the products of step k are issued (the
-    // compiler keeps the order of these instructions as written)
-    float s[4][4];
+    // scores of the warp's 16 rows against its half of the tile's 32 keys (the other warp of the pair does the other half); the
+    // fragments of step k + 1 are asked for before the products of step k are issued (the compiler keeps the order as written)
+    float s[2][4];
 #pragma unroll
-    for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    for (int n = 0; n < 2; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
     {
       const __nv_bfloat16* a_from = qs + (wm * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LAT_PITCH + (lane >> 4) * 8;
-      const __nv_bfloat16* b_from = kt + ((lane & 7) + (lane >> 4) * 8) * LAT_PITCH + ((lane >> 3) & 1) * 8;
-      unsigned a[2][4], b[2][2][4];
+      const __nv_bfloat16* b_from = kt + (wn * 16 + (lane & 7) + (lane >> 4) * 8) * LAT_PITCH + ((lane >> 3) & 1) * 8;
+      unsigned a[2][4], b[2][4];
       ldmatrix_x4(a[0], a_from);
-      ldmatrix_x4(b[0][0], b_from);
-      ldmatrix_x4(b[0][1], b_from + 16 * LAT_PITCH);
+      ldmatrix_x4(b[0], b_from);
 #pragma unroll
       for (int k = 0; k < LD / 16; ++k) {
         const int now = k & 1, next = now ^ 1;
         if (k + 1 < LD / 16) {
           ldmatrix_x4(a[next], a_from + (k + 1) * 16);
-          ldmatrix_x4(b[next][0], b_from + (k + 1) * 16);
-          ldmatrix_x4(b[next][1], b_from + 16 * LAT_PITCH + (k + 1) * 16);
+          ldmatrix_x4(b[next], b_from + (k + 1) * 16);
         }
-        mma_bf16(s[0], a[now], b[now][0][0], b[now][0][1]);
-        mma_bf16(s[1], a[now], b[now][0][2], b[now][0][3]);
-        mma_bf16(s[2], a[now], b[now][1][0], b[now][1][1]);
-        mma_bf16(s[3], a[now], b[now][1][2], b[now][1][3]);
+        mma_bf16(s[0], a[now], b[now][0], b[now][1]);
+        mma_bf16(s[1], a[now], b[now][2], b[now][3]);
       }
     }
-    // scale, mask, online softmax in base 2
+    // scale and mask; the rows' maxima over the warp's keys go to the pair's other warp and its come here
     float tile_top[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
+    for (int n = 0; n < 2; ++n) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = e >> 1;
-        const int j = key_tile * LAT_BN + n * 8 + (lane & 3) * 2 + (e & 1);
+        const int j = key_tile * LAT_BN + wn * 16 + n * 8 + (lane & 3) * 2 + (e & 1);
         const bool seen = live[i] && j <= pos[i] && (window <= 0 || j > pos[i] - window);
         s[n][e] = seen ? s[n][e] * scale_log2 : -INFINITY;
         tile_top[i] = fmaxf(tile_top[i], s[n][e]);
       }
     }
-    float rescale[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       tile_top[i] = fmaxf(tile_top[i], __shfl_xor_sync(0xffffffffu, tile_top[i], 1));
       tile_top[i] = fmaxf(tile_top[i], __shfl_xor_sync(0xffffffffu, tile_top[i], 2));
+      if ((lane & 3) == 0) pair_row[wm][wn][(lane >> 2) + 8 * i] = tile_top[i];
+    }
+    pair_barrier(wm);
+    float rescale[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      tile_top[i] = fmaxf(tile_top[i], pair_row[wm][wn ^ 1][(lane >> 2) + 8 * i]);
       const float new_top = fmaxf(top[i], tile_top[i]);
       rescale[i] = new_top == -INFINITY ? 1.f : exp2f(top[i] - new_top);   // top -inf: nothing was added yet, 0 * anything
       top[i] = new_top;
     }
+    // softmax weights of the warp's keys (float32, base 2): into the pair's tile of weights as bfloat16; the sums stay apart, each warp
+    // adding up its own keys, until the end
     float tile_sum[2] = {0.f, 0.f};
     const float use_top[2] = {top[0] == -INFINITY ? 0.f : top[0], top[1] == -INFINITY ? 0.f : top[1]};
 #pragma unroll
-    for (int n = 0; n < 4; ++n) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1;
-        const float p = exp2f(s[n][e] - use_top[i]);
-        s[n][e] = p;
-        tile_sum[i] += p;
-      }
+    for (int n = 0; n < 2; ++n) {
+      const float p0 = exp2f(s[n][0] - use_top[0]), p1 = exp2f(s[n][1] - use_top[0]);
+      const float p2 = exp2f(s[n][2] - use_top[1]), p3 = exp2f(s[n][3] - use_top[1]);
+      tile_sum[0] += p0 + p1;
+      tile_sum[1] += p2 + p3;
+      const int column = wn * 16 + n * 8 + (lane & 3) * 2;
+      *reinterpret_cast<unsigned*>(&pair_weights[wm][lane >> 2][column]) = pack_bf16(p0, p1);
+      *reinterpret_cast<unsigned*>(&pair_weights[wm][(lane >> 2) + 8][column]) = pack_bf16(p2, p3);
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -233,15 +241,17 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
       o[n][2] *= rescale[1];
       o[n][3] *= rescale[1];
     }
+    pair_barrier(wm);   // both halves of the weights are there; the maxima are read (they are written again only behind this barrier)
     // O += P V for the warp's half of the value columns, the next pair of value fragments asked for ahead of the products
     {
       const __nv_bfloat16* v_from = kt + ((lane & 7) + ((lane >> 3) & 1) * 8) * LAT_PITCH + wn * LAT_NV + (lane >> 4) * 8;
+      const __nv_bfloat16* p_from = &pair_weights[wm][(lane & 7) + ((lane >> 3) & 1) * 8][(lane >> 4) * 8];
       unsigned b[2][4];
       ldmatrix_x4_trans(b[0], v_from);
 #pragma unroll
       for (int step = 0; step < 2; ++step) {
-        const unsigned a[4] = {pack_bf16(s[2 * step][0], s[2 * step][1]), pack_bf16(s[2 * step][2], s[2 * step][3]),
-                               pack_bf16(s[2 * step + 1][0], s[2 * step + 1][1]), pack_bf16(s[2 * step + 1][2], s[2 * step + 1][3])};
+        unsigned a[4];
+        ldmatrix_x4(a, p_from + step * 16);
 #pragma unroll
         for (int n = 0; n < LAT_NV_TILES; n += 2) {
           const int now = (step * (LAT_NV_TILES / 2) + (n >> 1)) & 1, next = now ^ 1;   // the fragments' buffers take turns across both steps
@@ -254,6 +264,17 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
         }
       }
     }
+    // the weights are written again only behind the next tile's first pair barrier, which the other warp reaches with these reads done
+  }
+  // a row's sum is the sum of the pair's two halves
+  if (tile * LAT_BM + wm * 16 < packed) {
+    pair_barrier(wm);
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if ((lane & 3) == 0) pair_row[wm][wn][(lane >> 2) + 8 * i] = sum[i];
+    pair_barrier(wm);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) sum[i] += pair_row[wm][wn ^ 1][(lane >> 2) + 8 * i];
   }
   cp_async_wait<0>();
 

@@ -330,10 +330,24 @@ __global__ void __launch_bounds__(128) latent_attention_combine_kernel(const flo
   }
   __syncthreads();
   const float inv = total_shared > 0.f ? 1.f / total_shared : 0.f;
-  for (int e = threadIdx.x; e < LDV; e += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s) acc = fmaf(weight[s], scratch[((size_t)s * packed_rows + packed_row) * LDV + e], acc);
-    out[(size_t)packed_row * LDV + e] = __float2bfloat16_rn(acc * inv);
+  // a thread's (up to four) elements of all parts: the loads of several parts are in flight together
+  constexpr int PER_THREAD = (LDV + 127) / 128;
+  float acc[PER_THREAD];
+#pragma unroll
+  for (int k = 0; k < PER_THREAD; ++k) acc[k] = 0.f;
+#pragma unroll 4
+  for (int s = 0; s < splits; ++s) {
+    const float* part = scratch + ((size_t)s * packed_rows + packed_row) * LDV;
+#pragma unroll
+    for (int k = 0; k < PER_THREAD; ++k) {
+      const int e = threadIdx.x + k * 128;
+      if (e < LDV) acc[k] = fmaf(weight[s], part[e], acc[k]);
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < PER_THREAD; ++k) {
+    const int e = threadIdx.x + k * 128;
+    if (e < LDV) out[(size_t)packed_row * LDV + e] = __float2bfloat16_rn(acc[k] * inv);
   }
 }
 

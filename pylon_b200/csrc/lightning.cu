@@ -213,7 +213,7 @@ __global__ void lightning_scan_kernel(float* __restrict__ state, long long slot_
 
 // y[t] = o[t] / sqrt(mean(o[t]^2) + eps) * weight * sigmoid(gate[t]) over the `width` concatenated head outputs of a token.
 template <typename T>
-__global__ void __launch_bounds__(256) sigmoid_gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ carried,
+__global__ void __launch_bounds__(512) sigmoid_gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ carried,
                                                                     const int* __restrict__ token_segment, const T* __restrict__ gate, long long gate_ld,
                                                                     const float* __restrict__ weight, T* __restrict__ out, int width, float eps) {
   // carried (optional): what a token of a later segment of a long row reads of the state before its segment, to be added to o;
@@ -223,11 +223,13 @@ __global__ void __launch_bounds__(256) sigmoid_gated_rmsnorm_kernel(const float*
   const float* row = o + (size_t)t * width;
   const float* extra = carried != nullptr && token_segment[t] > 0 ? carried + (size_t)t * width : nullptr;
   float squares = 0.f;
+#pragma unroll 4
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const float x = row[i] + (extra ? extra[i] : 0.f);
     squares = fmaf(x, x, squares);
   }
   const float inv = rsqrtf(block_sum(squares, scratch) / width + eps);
+#pragma unroll 4
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const float gv = to_float<T>(gate[(size_t)t * gate_ld + i]);
     const float x = row[i] + (extra ? extra[i] : 0.f);
@@ -322,7 +324,7 @@ extern "C" int pylon_lightning_attention(const void* proj, long long ld, int q_c
   const size_t smem = lightning_shared_bytes(lanes);
   dim3 prepare_grid(num_tokens, heads);
   dim3 grid((vdim + columns - 1) / columns, heads, rows * segments);
-  const int norm_threads = width >= 1024 ? 256 : 128;
+  const int norm_threads = width >= 2048 ? 512 : (width >= 1024 ? 256 : 128);
   if (dtype == PYLON_DTYPE_F32)
     lightning_prepare_kernel<float><<<prepare_grid, LIGHTNING_THREADS, 0, stream>>>((const float*)proj, ld, q_col, k_col, v_col, qk, v, heads, dim, vdim, lanes);
   else

@@ -106,13 +106,16 @@ __global__ void __launch_bounds__(ROTARY_THREADS) latent_norm_rotate_write_kerne
   const int pos = positions[t];
   const T* src = down + (size_t)t * ld;
   float squares = 0.f;
+#pragma unroll 4
   for (int e = tid; e < q_rank; e += ROTARY_THREADS) {
     const float x = to_float<T>(src[e]);
     squares = fmaf(x, x, squares);
   }
   const float q_inv = rsqrtf(block_sum(squares, scratch) / (q_rank > 0 ? q_rank : 1) + eps);
+#pragma unroll 4
   for (int e = tid; e < q_rank; e += ROTARY_THREADS) cq[(size_t)t * q_rank + e] = from_float<T>(to_float<T>(src[e]) * q_inv * q_weight[e]);
   squares = 0.f;
+#pragma unroll 4
   for (int e = tid; e < kv_rank; e += ROTARY_THREADS) {
     const float x = to_float<T>(src[q_rank + e]);
     squares = fmaf(x, x, squares);
@@ -125,6 +128,7 @@ __global__ void __launch_bounds__(ROTARY_THREADS) latent_norm_rotate_write_kerne
     return;
   }
   T* dst = pages + ((size_t)page * page_size + pos % page_size) * (kv_rank + rot_dim);
+#pragma unroll 4
   for (int e = tid; e < kv_rank; e += ROTARY_THREADS) dst[e] = from_float<T>(to_float<T>(src[q_rank + e]) * kv_inv * kv_weight[e]);
   for (int e = tid; e < rot_dim; e += ROTARY_THREADS) turned[e] = to_float<T>(src[q_rank + kv_rank + e]);
   __syncthreads();

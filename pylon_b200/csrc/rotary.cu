@@ -99,42 +99,34 @@ __global__ void __launch_bounds__(ROTARY_THREADS) latent_norm_rotate_write_kerne
     T* __restrict__ pages, int num_pages, int q_rank, int kv_rank, int rot_dim, int* __restrict__ error_word) {
   extern __shared__ float rotary_shared[];
   float* scratch = rotary_shared;        // [34]
-  float* turned = rotary_shared + 34;    // [rot_dim]
+  float* staged = rotary_shared + 34;    // [q_rank + kv_rank + rot_dim]: the token's row, read from global memory once
+  float* turned = staged + q_rank + kv_rank;
   const int t = blockIdx.x, tid = threadIdx.x;
   const int row = token_row[t];
   if (row < 0) return;
   const int pos = positions[t];
   const T* src = down + (size_t)t * ld;
-  float squares = 0.f;
+  const int total = q_rank + kv_rank + rot_dim;
 #pragma unroll 4
-  for (int e = tid; e < q_rank; e += ROTARY_THREADS) {
-    const float x = to_float<T>(src[e]);
-    squares = fmaf(x, x, squares);
-  }
-  const float q_inv = rsqrtf(block_sum(squares, scratch) / (q_rank > 0 ? q_rank : 1) + eps);
-#pragma unroll 4
-  for (int e = tid; e < q_rank; e += ROTARY_THREADS) cq[(size_t)t * q_rank + e] = from_float<T>(to_float<T>(src[e]) * q_inv * q_weight[e]);
-  squares = 0.f;
-#pragma unroll 4
-  for (int e = tid; e < kv_rank; e += ROTARY_THREADS) {
-    const float x = to_float<T>(src[q_rank + e]);
-    squares = fmaf(x, x, squares);
-  }
-  const float kv_inv = rsqrtf(block_sum(squares, scratch) / kv_rank + eps);
+  for (int e = tid; e < total; e += ROTARY_THREADS) staged[e] = to_float<T>(src[e]);
   const int logical = pos / page_size;
   const int page = logical < table_width ? block_table[(size_t)row * table_width + logical] : -1;
+  __syncthreads();
+  float q_squares = 0.f, kv_squares = 0.f;
+  for (int e = tid; e < q_rank; e += ROTARY_THREADS) q_squares = fmaf(staged[e], staged[e], q_squares);
+  for (int e = tid; e < kv_rank; e += ROTARY_THREADS) kv_squares = fmaf(staged[q_rank + e], staged[q_rank + e], kv_squares);
+  const float q_inv = rsqrtf(block_sum(q_squares, scratch) / (q_rank > 0 ? q_rank : 1) + eps);
+  const float kv_inv = rsqrtf(block_sum(kv_squares, scratch) / kv_rank + eps);
+  for (int e = tid; e < q_rank; e += ROTARY_THREADS) cq[(size_t)t * q_rank + e] = from_float<T>(staged[e] * q_inv * q_weight[e]);
+  if (tid < 32 && rot > 0 && pos < table_positions)
+    rotate_pairs(turned, cos_table + (size_t)pos * (rot >> 1), sin_table + (size_t)pos * (rot >> 1), rot, layout, tid);
+  __syncthreads();
   if (page < 0 || page >= num_pages) {
     if (tid == 0 && error_word) atomicMax(error_word, PYLON_ERROR_BAD_PAGE);
     return;
   }
   T* dst = pages + ((size_t)page * page_size + pos % page_size) * (kv_rank + rot_dim);
-#pragma unroll 4
-  for (int e = tid; e < kv_rank; e += ROTARY_THREADS) dst[e] = from_float<T>(to_float<T>(src[q_rank + e]) * kv_inv * kv_weight[e]);
-  for (int e = tid; e < rot_dim; e += ROTARY_THREADS) turned[e] = to_float<T>(src[q_rank + kv_rank + e]);
-  __syncthreads();
-  if (tid < 32 && rot > 0 && pos < table_positions)
-    rotate_pairs(turned, cos_table + (size_t)pos * (rot >> 1), sin_table + (size_t)pos * (rot >> 1), rot, layout, tid);
-  __syncthreads();
+  for (int e = tid; e < kv_rank; e += ROTARY_THREADS) dst[e] = from_float<T>(staged[q_rank + e] * kv_inv * kv_weight[e]);
   for (int e = tid; e < rot_dim; e += ROTARY_THREADS) dst[kv_rank + e] = from_float<T>(turned[e]);
 }
 
@@ -197,7 +189,8 @@ extern "C" int pylon_latent_norm_rotate_write(const void* down, long long ld, vo
   if (q_rank < 0 || kv_rank < 1 || rot_dim < 0 || rot_dim > 8192) PYLON_REFUSE("latent_norm_rotate_write: ranks %d / %d, %d rotated", q_rank, kv_rank, rot_dim);
   if (rot < 0 || rot > rot_dim || rot % 2 || (rot > 0 && (!cos_table || !sin_table))) PYLON_REFUSE("latent_norm_rotate_write: %d rotated elements of %d", rot, rot_dim);
   if (page_size < 1 || table_width < 1) PYLON_REFUSE("latent_norm_rotate_write: page size %d, table width %d", page_size, table_width);
-  const size_t smem = (size_t)(34 + rot_dim) * sizeof(float);
+  const size_t smem = (size_t)(34 + q_rank + kv_rank + rot_dim) * sizeof(float);
+  if (smem > 48 * 1024) PYLON_REFUSE("latent_norm_rotate_write: a row of %d numbers is too wide", q_rank + kv_rank + rot_dim);
   if (dtype == PYLON_DTYPE_F32)
     latent_norm_rotate_write_kernel<float><<<num_tokens, ROTARY_THREADS, smem, stream>>>(
         (const float*)down, ld, (float*)cq, q_weight, kv_weight, eps, cos_table, sin_table, rot, layout, table_positions, positions, token_row,

@@ -18,8 +18,8 @@ decode steps) at B = 1, 8, 64 with its share of the HBM roofline; the output rat
 serving workloads at the 8B and 14B shapes; and a full-depth float32 run at the 14B shape with
 its largest logit error against the plain implementation.
 
-``--workload designs`` is another measurement with a line of its own: Vopepel beside Qwen3 dense at equal width, depth, heads,
-feed-forward and vocabulary (sizes ``2k`` and ``4k``): prefill of a 2,048-token prompt, decode at batch 8 and a context of 2,048,
+``--workload designs`` is another measurement with a line of its own: Vopepel and Fikerax beside Qwen3 dense at equal width, depth,
+heads, feed-forward and vocabulary (sizes ``2k`` and ``4k``; ``--designs`` picks among the three): prefill of a 2,048-token prompt, decode at batch 8 and a context of 2,048,
 and the time of every kernel entry point in one step of each kind.
 """
 from __future__ import annotations
@@ -475,7 +475,7 @@ def run_serving_workload(name: str, torch) -> dict:
 
 
 # ---------------------------------------------------------------------------------------
-# Vopepel beside Qwen3 at equal size (--workload designs)
+# Vopepel and Fikerax beside Qwen3 at equal size (--workload designs)
 # ---------------------------------------------------------------------------------------
 DESIGN_SIZES = {
     # width, layers, heads / kv heads / head size of the attention, inner width of the feed-forward, vocabulary

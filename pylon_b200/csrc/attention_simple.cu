@@ -1,5 +1,5 @@
-// Paged causal attention, the plain form: one block per (token, query head), any head size
-// up to 512, any page size, any group size, optional window or chunks of positions, optional soft
+// Paged causal attention, the plain form: one block per (token, query head), any key size
+// up to 2,048 and value size up to 512, any page size, any group size, optional window or chunks of positions, optional soft
 // cap on the scores, values of another width than the keys.  It is the attention of the
 // true 32-bit path and the fall-back of the bfloat16 path for head sizes the tensor-core
 // kernel is not built for.  Scores, softmax and the weighted sum are float32.
